@@ -1,9 +1,10 @@
 """The cache of a model on the device: page pools per group, one view per cache
-id, and the fixed-size state of every request slot
+id (keys and values, or one plane of rows for a part that stores a latent per
+token), and the fixed-size state of every request slot
 (python/helios/exec/paged_attn.py:25-115 holds the same bytes, one object per layer;
 python/helios/exec/runner.py:64-74 allocates them).
 
-Layout of a group: ``[cache ids in the group, 2 (k, v), pages, kv heads,
+Layout of a group: ``[cache ids in the group, planes (k, v; or 1), pages, kv heads,
 page_size, head_dim]``; one page id addresses the same page in every cache id of
 the group, and a (page, kv head) tile of ``page_size x head_dim`` is contiguous.
 """
@@ -46,7 +47,7 @@ def bytes_per_page(plan: ModelPlan, page_size: int, dtype_bytes: int) -> List[in
     counts = [0] * len(specs)
     for g, _ in where.values():
         counts[g] += 1
-    return [2 * counts[g] * page_size * s.num_kv_heads * s.head_dim * dtype_bytes
+    return [s.planes * counts[g] * page_size * s.num_kv_heads * s.head_dim * dtype_bytes
             for g, s in enumerate(specs)]
 
 
@@ -105,17 +106,19 @@ class KVCacheManager(CacheLayout):
         self.storage: List[torch.Tensor] = []
         for g, spec in enumerate(specs):
             # one page more than the pool hands out: padding rows of captured graphs write there
-            shape = (counts[g], 2, num_pages[g] + 1, spec.num_kv_heads, page_size, spec.head_dim)
+            shape = (counts[g], spec.planes, num_pages[g] + 1, spec.num_kv_heads, page_size, spec.head_dim)
             t = torch.empty(shape, dtype=dtype, device=self.device)
             t.fill_(poison) if poison is not None else t.zero_()
             self.storage.append(t)
-        # fixed-size state per request slot, for the mixers that keep one
+        # fixed-size state per request slot, for the mixers that keep one; one row more than
+        # there are slots: the padding requests of captured steps read and write that one
+        self.pad_slot = max_slots
         self.states: Dict[int, torch.Tensor] = {}
         for entry, run in enumerate(plan.schedule):
             mixer = plan.layers[run.layer].mixer
             spec = mixer.state_spec() if mixer is not None else None
             if spec is not None and plan.cache_id(entry) == entry:
-                self.states[entry] = torch.zeros((max_slots,) + tuple(spec.shape),
+                self.states[entry] = torch.zeros((max_slots + 1,) + tuple(spec.shape),
                                                  dtype=spec.dtype, device=self.device)
         # ... and for the other parts of a block that keep one (a feed-forward, say):
         # cache id -> {id(part): [slots, *shape]}
@@ -125,7 +128,7 @@ class KVCacheManager(CacheLayout):
                 continue
             for part, spec in plan.layers[run.layer].state_specs():
                 self.other_states.setdefault(entry, {})[id(part)] = torch.zeros(
-                    (max_slots,) + tuple(spec.shape), dtype=spec.dtype, device=self.device)
+                    (max_slots + 1,) + tuple(spec.shape), dtype=spec.dtype, device=self.device)
         self._views: Dict[int, LayerCache] = {}
         #: per group, the id of the spare page no request ever gets
         self.pad_pages: List[int] = list(num_pages)
@@ -139,7 +142,8 @@ class KVCacheManager(CacheLayout):
             if cid not in self._where:
                 return None
             g, idx = self._where[cid]
-            view = LayerCache(self.storage[g][idx, 0], self.storage[g][idx, 1], g,
+            planes = self.storage[g][idx]
+            view = LayerCache(planes[0], planes[1] if planes.shape[0] > 1 else None, g,
                               self.page_size, write=self.plan.schedule[entry].writes_cache)
             self._views[entry] = view
         return view

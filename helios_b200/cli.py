@@ -46,12 +46,12 @@ def cmd_info(args: argparse.Namespace) -> int:
 
     from .cache.manager import bytes_per_page, cache_groups_of, pool_sizes_for_bytes
     from .config.model_config import read_config_json
-    from .config.registry import resolve_architecture
+    from .config.registry import resolve_architecture, typed_config
     from .weights.loader import expected_tensors
 
     cfg_json = read_config_json(Path(args.model))
     arch = resolve_architecture(cfg_json)
-    plan = arch.build_plan(arch.parse_config(cfg_json))
+    plan = arch.build_plan(typed_config(arch, cfg_json, args.model))
     stored = {n: spec for n, (_p, _l, spec) in expected_tensors(plan).items() if n not in plan.tied}
     params = sum(prod(spec.shape) for spec in stored.values())
     print(f"{args.model}: {arch.name}")

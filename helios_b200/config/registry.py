@@ -23,16 +23,19 @@ class Architecture:
     # intermediate_size, layers, heads, kv_heads, head_dim, max_pos, rope_theta, rope_scaling,
     # rms_eps, sliding_window, max_window_layers, tie; None where not given) -> config.json
     toy_config: Optional[Callable[[Dict[str, Any]], Dict[str, Any]]] = None
+    # (typed config, checkpoint tensor name -> shape) -> typed config: for a design whose
+    # config.json leaves sizes to the shapes of its tensors
+    sizes_from_tensors: Optional[Callable[[Any, Dict[str, tuple]], Any]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
 def register_architecture(name: str, parse_config, build_plan, *, toy_config=None,
-                          replace: bool = False) -> None:
+                          sizes_from_tensors=None, replace: bool = False) -> None:
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is already registered")
-    _ARCHITECTURES[name] = Architecture(name, parse_config, build_plan, toy_config)
+    _ARCHITECTURES[name] = Architecture(name, parse_config, build_plan, toy_config, sizes_from_tensors)
 
 
 def unregister_architecture(name: str) -> None:
@@ -65,6 +68,8 @@ def find_architecture(name: str) -> Architecture:
 def resolve_architecture(cfg: Dict[str, Any]) -> Architecture:
     _builtin()
     archs = cfg.get("architectures") or []
+    if not archs and isinstance(cfg.get("architecture"), str):
+        archs = [cfg["architecture"]]            # a file that names its one design outright
     if not archs:
         raise ConfigError("config.json lacks 'architectures'; known: "
                           + ", ".join(known_architectures()))
@@ -75,8 +80,18 @@ def resolve_architecture(cfg: Dict[str, Any]) -> Architecture:
                       + ", ".join(known_architectures()))
 
 
+def typed_config(arch: Architecture, cfg: Dict[str, Any], model_dir=None):
+    """``arch.parse_config(cfg)``, completed from the tensor shapes of the checkpoint in
+    ``model_dir`` where the architecture asks for them (and a folder is given)."""
+    typed = arch.parse_config(cfg)
+    if arch.sizes_from_tensors is not None and model_dir is not None:
+        from ..weights.loader import tensor_shapes
+        typed = arch.sizes_from_tensors(typed, tensor_shapes(model_dir))
+    return typed
+
+
 def load_config(model_dir):
     """Typed configuration of the model folder, chosen by its ``architectures``."""
     cfg = read_config_json(model_dir)
     arch = resolve_architecture(cfg)
-    return arch.parse_config(cfg)
+    return typed_config(arch, cfg, model_dir)

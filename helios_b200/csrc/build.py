@@ -39,6 +39,9 @@ LIBRARIES: Dict[str, str] = {
     "gemm_bf16": "gemm_bf16.cu",
     "gemm_bf16_noalloc": "gemm_bf16_noalloc.cu",
     "sampling": "sampling.cu",
+    "latent_attention": "latent_attention.cu",
+    "delta_rule": "delta_rule.cu",
+    "moe": "moe.cu",
 }
 _HEADERS = ["common.cuh", "tcgen05.cuh"]
 # further files a library's source includes

@@ -205,7 +205,8 @@ HB_EXPORT int hb_rmsnorm(void* out, const void* x, const float* weight, int n, i
 // same table for every position up to max_position_embeddings).
 __global__ void rotary_table_kernel(float* __restrict__ cos_out, float* __restrict__ sin_out,
                                     const int* __restrict__ positions,
-                                    const double* __restrict__ inv_freq, int T, int half) {
+                                    const double* __restrict__ inv_freq, int T, int half,
+                                    double factor) {
   pdl_launch_dependents();
   pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -213,16 +214,17 @@ __global__ void rotary_table_kernel(float* __restrict__ cos_out, float* __restri
   const int t = idx / half, j = idx - t * half;
   double s, c;
   sincos((double)positions[t] * inv_freq[j], &s, &c);
-  cos_out[idx] = (float)c;
-  sin_out[idx] = (float)s;
+  cos_out[idx] = (float)(c * factor);
+  sin_out[idx] = (float)(s * factor);
 }
 
 HB_EXPORT int hb_rotary_table(float* cos_out, float* sin_out, const int* positions,
-                              const double* inv_freq, int T, int half, cudaStream_t stream) {
+                              const double* inv_freq, int T, int half, double factor,
+                              cudaStream_t stream) {
   if (T <= 0 || half <= 0) return HB_OK;
   const int total = T * half;
   hb_launch(rotary_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, cos_out, sin_out, positions,
-                                                               inv_freq, T, half);
+                                                               inv_freq, T, half, factor);
   return hb_check_launch();
 }
 
@@ -401,5 +403,94 @@ HB_EXPORT int hb_silu_mul(void* out, const void* gate_up, int T, int I, int act_
   if (blocks > 148 * 16) blocks = 148 * 16;
   HB_DISPATCH_DTYPE(act_dt, TA,
     hb_launch(silu_mul_kernel<TA>, dim3((unsigned)blocks), dim3(threads), 0, stream, (TA*)out, (const TA*)gate_up, total, I));
+  return hb_check_launch();
+}
+
+
+// ---------------------------------------------------------------- gated activations
+// out[t, i] = act(gu[t, i]) * gu[t, I + i] for a feed-forward whose gate and up rows come
+// out of one product.  kind 0: silu(g) * u.  kind 1: the tanh form of gelu,
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u.  kind 2: the clamped form
+// g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1).
+enum { HB_GLU_SILU = 0, HB_GLU_GELU_TANH = 1, HB_GLU_CLAMPED_SWISH = 2 };
+
+__device__ __forceinline__ float glu_value(float g, float u, int kind, float limit) {
+  if (kind == HB_GLU_GELU_TANH) {
+    const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.f + tanhf(z)) * u;
+  }
+  if (kind == HB_GLU_CLAMPED_SWISH) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+  }
+  return g / (1.f + expf(-g)) * u;
+}
+
+template <typename T>
+__global__ void glu_act_kernel(T* __restrict__ out, const T* __restrict__ gu, size_t total, int I,
+                               int kind, float limit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    out[idx] = from_float<T>(glu_value(to_float(gu[t * 2 * I + i]), to_float(gu[t * 2 * I + I + i]),
+                                       kind, limit));
+  }
+}
+
+HB_EXPORT int hb_glu_act(void* out, const void* gate_up, int T, int I, int kind, float limit,
+                         int act_dt, cudaStream_t stream) {
+  if (T <= 0) return HB_OK;
+  if (kind < 0 || kind > 2) return HB_BAD_ARGUMENT;
+  const size_t total = (size_t)T * I;
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(glu_act_kernel<TA>, dim3((unsigned)blocks), dim3(threads), 0, stream, (TA*)out,
+              (const TA*)gate_up, total, I, kind, limit));
+  return hb_check_launch();
+}
+
+// ---------------------------------------------------------------- norm on a sublayer's output
+// residual[r, :] += y[r, :] / sqrt(mean(y[r, :]^2) + eps) * weight (float32), for a block
+// that norms what a sublayer returns instead of what it reads; `copy` (may be null)
+// receives the new residual row in the activation dtype, which is what the next sublayer
+// reads.  With y == null only the copy is made.
+template <typename TY, typename TC>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_kernel(float* __restrict__ residual, const TY* __restrict__ y,
+                   const float* __restrict__ weight, TC* __restrict__ copy, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  float* res = residual + (size_t)blockIdx.x * H;
+  TC* cp = copy ? copy + (size_t)blockIdx.x * H : nullptr;
+  if (y == nullptr) {
+    for (int c = threadIdx.x; c < H; c += blockDim.x) cp[c] = from_float<TC>(res[c]);
+    return;
+  }
+  const TY* yr = y + (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) { const float v = to_float(yr[c]); ss += v * v; }
+  const float rstd = rsqrtf(block_sum(ss, scratch) / (float)H + eps);
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float v = res[c] + to_float(yr[c]) * rstd * weight[c];
+    res[c] = v;
+    if (cp) cp[c] = from_float<TC>(v);
+  }
+}
+
+HB_EXPORT int hb_rmsnorm_add(float* residual, const void* y, const float* weight, void* copy,
+                             int n, int H, float eps, int y_dt, int copy_dt, cudaStream_t stream) {
+  if (n <= 0) return HB_OK;
+  if (y == nullptr && copy == nullptr) return HB_OK;
+  HB_DISPATCH_DTYPE(y_dt, TY,
+    HB_DISPATCH_DTYPE(copy_dt, TC,
+      hb_launch(rmsnorm_add_kernel<TY, TC>, dim3(n), dim3(256), 0, stream, residual, (const TY*)y,
+                weight, (TC*)copy, H, eps)));
   return hb_check_launch();
 }

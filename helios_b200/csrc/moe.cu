@@ -1,0 +1,147 @@
+// Routed feed-forward: every token runs `top` of `experts` small gated feed-forward layers.
+//
+//   z = W_router h (float32), s = sigmoid(z); the `top` experts with the largest s are
+//   chosen (the lower index on a tie); an expert's weight is its s, not renormalised, and
+//   multiplies the expert's INPUT:  out = sum over chosen e of expert_e(s_e * h).
+//
+// `moe_topk` picks experts and weights.  `moe_expert_rows` runs one (token, choice) pair per
+// block, streaming that expert's rows (steps of few tokens, where every expert's weights
+// are read about once); `moe_combine` adds a token's choices in the order of the choice.
+// The gate is the clamped form of `glu_value` in elementwise.cu:
+// g' = min(g, limit), u' = clamp(u, -limit, limit), y = g' sigmoid(1.702 g') (u' + 1).
+#include "common.cuh"
+
+constexpr int MOE_MAX_TOP = 16;
+
+__global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weights,
+                                const float* __restrict__ logits, int n_tokens, int experts,
+                                int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tokens) return;
+  const float* z = logits + (size_t)t * experts;
+  int chosen[MOE_MAX_TOP];
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int at = 0;
+    bool found = false;
+    for (int e = 0; e < experts; ++e) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= (chosen[j] == e);
+      if (taken) continue;
+      const float s = 1.f / (1.f + expf(-z[e]));
+      if (!found || s > best) { best = s; at = e; found = true; }
+    }
+    chosen[k] = at;
+    ids[(size_t)t * top + k] = at;
+    weights[(size_t)t * top + k] = best;
+  }
+}
+
+HB_EXPORT int hb_moe_topk(int* ids, float* weights, const float* logits, int n_tokens, int experts,
+                          int top, cudaStream_t stream) {
+  if (n_tokens <= 0) return HB_OK;
+  if (experts <= 0 || top <= 0 || top > experts || top > MOE_MAX_TOP) return HB_BAD_ARGUMENT;
+  hb_launch(moe_topk_kernel, dim3((n_tokens + 127) / 128), dim3(128), 0, stream, ids, weights,
+            logits, n_tokens, experts, top);
+  return hb_check_launch();
+}
+
+// w_gate_up [experts, 2 ff, width] (gate rows, then up rows), w_down [experts, width, ff].
+// h [T, width] in the activation dtype.  partial [T * top, width] float32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_expert_rows_kernel(float* __restrict__ partial, const T* __restrict__ h,
+                       const T* __restrict__ w_gate_up, const T* __restrict__ w_down,
+                       const int* __restrict__ ids, const float* __restrict__ weights, int top,
+                       int width, int ff, float limit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* x = sm;                 // [width]
+  float* y = sm + width;         // [ff]
+  const int pair = blockIdx.x;
+  const int e = ids[pair];
+  const float w = weights[pair];
+  const int t = pair / top;
+  const T* hr = h + (size_t)t * width;
+  // the expert's input, rounded as the activation dtype rounds it
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    x[c] = to_float(from_float<T>(w * to_float(hr[c])));
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const T* wg = w_gate_up + (size_t)e * 2 * ff * width;
+  for (int f = warp; f < ff; f += n_warps) {
+    const T* gr = wg + (size_t)f * width;
+    const T* ur = wg + (size_t)(ff + f) * width;
+    float g = 0.f, u = 0.f;
+    for (int c = lane; c < width; c += 32) {
+      g = fmaf(to_float(gr[c]), x[c], g);
+      u = fmaf(to_float(ur[c]), x[c], u);
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) {
+      g = fminf(to_float(from_float<T>(g)), limit);
+      u = fminf(fmaxf(to_float(from_float<T>(u)), -limit), limit);
+      y[f] = to_float(from_float<T>(g / (1.f + expf(-1.702f * g)) * (u + 1.f)));
+    }
+  }
+  __syncthreads();
+  const T* wd = w_down + (size_t)e * width * ff;
+  float* dst = partial + (size_t)pair * width;
+  for (int c = warp; c < width; c += n_warps) {
+    const T* dr = wd + (size_t)c * ff;
+    float a = 0.f;
+    for (int f = lane; f < ff; f += 32) a = fmaf(to_float(dr[f]), y[f], a);
+    a = warp_sum(a);
+    if (lane == 0) dst[c] = a;
+  }
+}
+
+HB_EXPORT int hb_moe_expert_rows(float* partial, const void* h, const void* w_gate_up,
+                                 const void* w_down, const int* ids, const float* weights,
+                                 int n_tokens, int top, int width, int ff, float limit, int act_dt,
+                                 cudaStream_t stream) {
+  if (n_tokens <= 0) return HB_OK;
+  if (top <= 0 || width <= 0 || ff <= 0) return HB_BAD_ARGUMENT;
+  const size_t smem = (size_t)(width + ff) * sizeof(float);
+  if (smem > 200 * 1024) return HB_BAD_ARGUMENT;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(moe_expert_rows_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem);
+    hb_launch(moe_expert_rows_kernel<TA>, dim3(n_tokens * top), dim3(256), smem, stream,
+              partial, (const TA*)h, (const TA*)w_gate_up, (const TA*)w_down, ids, weights, top, width,
+              ff, limit));
+  return hb_check_launch();
+}
+
+// out[t, :] = sum over k of partial[t * top + k, :], k = 0..top-1 in that order
+template <typename T>
+__global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ partial,
+                                   size_t total, int width, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / width;
+    const int c = (int)(idx - t * width);
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) a += partial[(t * top + k) * width + c];
+    out[idx] = from_float<T>(a);
+  }
+}
+
+HB_EXPORT int hb_moe_combine(void* out, const float* partial, int n_tokens, int width, int top,
+                             int act_dt, cudaStream_t stream) {
+  if (n_tokens <= 0) return HB_OK;
+  const size_t total = (size_t)n_tokens * width;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(moe_combine_kernel<TA>, dim3((unsigned)blocks), dim3(256), 0, stream, (TA*)out,
+              partial, total, width, top));
+  return hb_check_launch();
+}

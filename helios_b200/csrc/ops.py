@@ -167,16 +167,17 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------ rotary + cache write
-def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor):
-    """cos and sin [T, rot/2] (float32) of position * inv_freq, computed in float64."""
+def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor, factor: float = 1.0):
+    """cos and sin [T, rot/2] (float32) of position * inv_freq, computed in float64 and
+    multiplied by ``factor`` (the attention factor of a scaled encoding; 1 for none)."""
     _check(positions, "positions", torch.int32, 1)
     _check(inv_freq, "inv_freq", torch.float64, 1)
     T, half = positions.numel(), inv_freq.numel()
     cos = torch.empty((T, half), dtype=torch.float32, device=positions.device)
     sin = torch.empty_like(cos)
     f = _fn("elementwise", "hb_rotary_table",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _run(f(_p(cos), _p(sin), _p(positions), _p(inv_freq), T, half, _stream()), "rotary_table")
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_double, c_void_p])
+    _run(f(_p(cos), _p(sin), _p(positions), _p(inv_freq), T, half, float(factor), _stream()), "rotary_table")
     return cos, sin
 
 
@@ -1053,3 +1054,274 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                                       window, scale)
     return attention_generic(qkv, k_pages, v_pages, block_table, ctx.seq_of_token, ctx.positions,
                              num_heads, num_kv_heads, head_dim, page_size, window, scale)
+
+
+# ------------------------------------------------------------------ gated activations, post-norm
+GLU_KINDS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+
+def glu_act(gate_up: torch.Tensor, kind: str, limit: float = 0.0) -> torch.Tensor:
+    """act(gate) * up for ``gate_up`` = [T, 2 I] (gate columns first).  ``kind``: "silu",
+    "gelu_tanh" (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u) or "clamped_swish"
+    (g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1))."""
+    _check(gate_up, "gate_up", None, 2)
+    if kind not in GLU_KINDS:
+        raise KernelError(f"gated activation {kind!r} is not one of {sorted(GLU_KINDS)}")
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gate_up must have an even width")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn("elementwise", "hb_glu_act",
+            [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _run(f(_p(out), _p(gate_up), T, two_i // 2, GLU_KINDS[kind], float(limit), _dt(gate_up.dtype),
+           _stream()), "glu_act")
+    return out
+
+
+def rmsnorm_add(residual: torch.Tensor, y: Optional[torch.Tensor], weight: Optional[torch.Tensor],
+                eps: float, copy_dtype: Optional[torch.dtype]) -> Optional[torch.Tensor]:
+    """``residual += y / sqrt(mean(y^2) + eps) * weight`` row by row, in float32 and in place
+    (a block that norms a sublayer's OUTPUT).  With ``copy_dtype`` other than float32 the new
+    residual is also returned in that dtype (what the next sublayer reads); for float32 the
+    residual itself is returned.  ``y`` None: only the copy."""
+    _check(residual, "residual", torch.float32, 2)
+    n, H = residual.shape
+    if y is not None:
+        _check(y, "y", None, 2)
+        _check(weight, "weight", torch.float32, 1)
+        if tuple(y.shape) != (n, H) or weight.numel() != H:
+            raise KernelError(f"y {tuple(y.shape)} / weight {weight.numel()} do not match residual {(n, H)}")
+    copy = None
+    if copy_dtype is not None and copy_dtype != torch.float32:
+        copy = torch.empty((n, H), dtype=copy_dtype, device=residual.device)
+    if y is not None or copy is not None:
+        f = _fn("elementwise", "hb_rmsnorm_add",
+                [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p])
+        _run(f(_p(residual), _p(y), _p(weight), _p(copy), n, H, float(eps),
+               _dt(y.dtype) if y is not None else _F32, _dt(copy.dtype) if copy is not None else _F32,
+               _stream()), "rmsnorm_add")
+    if copy_dtype is None:
+        return None
+    return residual if copy is None else copy
+
+
+# ------------------------------------------------------------------ attention over a latent cache
+_LONG = ctypes.c_long
+
+
+def latent_prepare(proj: torch.Tensor, pages: Optional[torch.Tensor], norm_weight: torch.Tensor,
+                   cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
+                   seq_of_token: torch.Tensor, block_table: torch.Tensor, heads: int, nope: int,
+                   rot: int, rank: int, page_size: int, eps: float, write_cache: bool = True) -> None:
+    """``proj`` [T, heads (nope + rot) + rank + rot] = [q | latent | shared key part], straight
+    from the projection.  The latent is RMS-normed (float32 statistics, ``norm_weight``), the
+    shared key part rotated (interleaved pairs, cos/sin [T, nrot / 2] over its first nrot
+    values) and both stored as one row [rank + rot] of ``pages`` [pages, 1, page_size, rank +
+    rot]; the queries' rotated parts are rotated in place."""
+    _check(proj, "proj", None, 2)
+    _check(norm_weight, "norm_weight", torch.float32, 1)
+    _check(cos, "cos", torch.float32, 2)
+    _check(sin, "sin", torch.float32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    T = proj.shape[0]
+    if proj.shape[1] != heads * (nope + rot) + rank + rot:
+        raise KernelError(f"proj has {proj.shape[1]} columns, expected {heads * (nope + rot) + rank + rot}")
+    nrot = 2 * cos.shape[1]
+    if cos.shape != sin.shape or cos.shape[0] != T or nrot > rot:
+        raise KernelError(f"cos/sin tables {tuple(cos.shape)} do not fit {T} tokens and {rot} rotated values")
+    if norm_weight.numel() != rank:
+        raise KernelError(f"norm weight has {norm_weight.numel()} entries for rank {rank}")
+    if write_cache:
+        _check(pages, "pages", proj.dtype, 4)
+        if tuple(pages.shape[1:]) != (1, page_size, rank + rot):
+            raise KernelError(f"pages have shape {tuple(pages.shape)}, expected [pages, 1, {page_size}, {rank + rot}]")
+    f = _fn("latent_attention", "hb_latent_prepare",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+    _run(f(_p(proj), proj.shape[1], _p(pages) if write_cache else 0, _p(norm_weight), _p(cos), _p(sin),
+           _p(positions), _p(seq_of_token), _p(block_table), block_table.shape[1], T, heads, nope, rot,
+           rank, nrot, page_size, float(eps), 1 if write_cache else 0, _dt(proj.dtype), _stream()),
+         "latent_prepare")
+
+
+#: from this many tokens on the per-head products of a bfloat16 step go to the library's
+#: batched product (tensor cores); below, and in float32, this package's FMA kernel streams
+#: the small matrices once
+HEAD_GEMM_LIBRARY_TOKENS = 33
+
+
+def head_gemm(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[t, h, n] = sum_k a[t, h, k] w[h, n, k]: one small matrix per head.  ``a`` is a view
+    [T, heads, K] whose last dimension is contiguous (a slice of wider rows is fine); ``w``
+    [heads, N, K] contiguous.  Returns [T, heads, N] (a view whose last dimension is
+    contiguous), float32 sums."""
+    if a.dim() != 3 or w.dim() != 3 or a.shape[1] != w.shape[0] or a.shape[2] != w.shape[2]:
+        raise KernelError(f"head_gemm: a {tuple(a.shape)} and w {tuple(w.shape)} do not fit")
+    if not a.is_cuda or not w.is_cuda or a.dtype != w.dtype or a.stride(2) != 1 or not w.is_contiguous():
+        raise KernelError("head_gemm: tensors must be CUDA, of one dtype, rows contiguous")
+    T, H, K = a.shape
+    N = w.shape[1]
+    if a.dtype == torch.bfloat16 and T >= HEAD_GEMM_LIBRARY_TOKENS:
+        return torch.bmm(a.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1)
+    out = torch.empty((T, H, N), dtype=a.dtype, device=a.device)
+    f = _fn("latent_attention", "hb_head_gemm",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, _LONG, _LONG, _LONG, c_int, _LONG, _LONG,
+             _LONG, c_int, c_void_p])
+    _run(f(_p(out), _p(a), _p(w), T, N, K, a.stride(0), K, H * N, H, a.stride(1), N * K, N,
+           _dt(a.dtype), _stream()), "head_gemm")
+    return out
+
+
+def latent_attention(ctx, q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tensor,
+                     block_table: torch.Tensor, rank: int, rot: int, page_size: int,
+                     scale: float) -> torch.Tensor:
+    """Causal attention of every token of the step over its request's latent rows.  ``q_lat``
+    [T, heads, rank] and ``q_rot`` [T, heads, rot] are views with a contiguous last dimension;
+    ``pages`` [pages, 1, page_size, rank + rot].  Returns [T, heads, rank] (softmax-weighted
+    sums of the rows' first ``rank`` values)."""
+    _check(pages, "pages", q_lat.dtype, 4)
+    _check(block_table, "block_table", torch.int32, 2)
+    if q_lat.dim() != 3 or q_rot.dim() != 3 or q_lat.stride(2) != 1 or q_rot.stride(2) != 1 \
+            or q_lat.shape[:2] != q_rot.shape[:2] or q_lat.shape[2] != rank or q_rot.shape[2] != rot \
+            or q_rot.dtype != q_lat.dtype:
+        raise KernelError(f"latent_attention: q_lat {tuple(q_lat.shape)} / q_rot {tuple(q_rot.shape)} "
+                          f"do not fit rank {rank}, rot {rot}")
+    if tuple(pages.shape[1:]) != (1, page_size, rank + rot):
+        raise KernelError(f"pages have shape {tuple(pages.shape)}, expected [pages, 1, {page_size}, {rank + rot}]")
+    if rank > 512 or rank + rot > 1024:
+        raise KernelError(f"latent rank {rank} (at most 512) or row {rank + rot} (at most 1024) is not supported")
+    T, H = q_lat.shape[:2]
+    out = torch.empty((T, H, rank), dtype=q_lat.dtype, device=q_lat.device)
+    f = _fn("latent_attention", "hb_latent_attention",
+            [c_void_p, c_void_p, _LONG, _LONG, c_void_p, _LONG, _LONG, c_void_p, c_void_p, c_int, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _run(f(_p(out), _p(q_lat), q_lat.stride(0), q_lat.stride(1), _p(q_rot), q_rot.stride(0),
+           q_rot.stride(1), _p(pages), _p(block_table), block_table.shape[1], _p(ctx.seq_of_token),
+           _p(ctx.positions), T, H, rank, rot, page_size, float(scale), _dt(q_lat.dtype), _stream()),
+         "latent_attention")
+    return out
+
+
+# ------------------------------------------------------------------ gated delta rule
+def causal_conv_silu(ctx, x: torch.Tensor, channels: int, weight: torch.Tensor,
+                     conv_state: torch.Tensor) -> torch.Tensor:
+    """silu of a short causal convolution over time, per channel, of the first ``channels``
+    columns of ``x`` [T, ld]; ``weight`` [channels, taps] float32 (last column: the current
+    token).  ``conv_state`` [slots, channels * (taps - 1)] float32 (rows may be strided) holds
+    every request's last taps - 1 inputs: read for the tokens before the step's first, and
+    left holding the step's last ones."""
+    _check(x, "x", None, 2)
+    _check(weight, "weight", torch.float32, 2)
+    taps = weight.shape[1]
+    if weight.shape[0] != channels or x.shape[1] < channels:
+        raise KernelError(f"conv weight {tuple(weight.shape)} / x {tuple(x.shape)} do not fit {channels} channels")
+    if conv_state.dtype != torch.float32 or conv_state.dim() != 2 or conv_state.stride(1) != 1 \
+            or conv_state.shape[1] != channels * (taps - 1):
+        raise KernelError(f"conv state {tuple(conv_state.shape)} does not fit {channels} channels x {taps - 1}")
+    T = x.shape[0]
+    out = torch.empty((T, channels), dtype=x.dtype, device=x.device)
+    f = _fn("delta_rule", "hb_causal_conv_silu",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, _LONG, c_void_p, c_void_p, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(x), x.shape[1], _p(weight), _p(conv_state), conv_state.stride(0),
+           _p(ctx.seq_of_token), _p(ctx.cu_tokens), _p(ctx.slots), T, ctx.num_seqs, channels, taps,
+           _dt(x.dtype), _stream()), "causal_conv_silu")
+    return out
+
+
+def delta_rule(ctx, qkv: torch.Tensor, offsets, beta_raw: torch.Tensor, a_raw: torch.Tensor,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, heads: int,
+               kv_heads: int, dk: int, dv: int) -> torch.Tensor:
+    """The gated delta rule over the step's tokens, request by request, from the state each
+    request's slot holds (``state`` [slots, heads * dk * dv] float32, rows may be strided;
+    left updated).  ``qkv`` [T, .] holds q, k (kv_heads x dk) and v (heads x dv) at the column
+    ``offsets`` (q, k, v); ``beta_raw`` [T, .] one column per head before the sigmoid;
+    ``a_raw`` [T, heads * dk] before dt_bias and softplus (both views with contiguous rows).
+    Returns o [T, heads * dv] float32."""
+    _check(qkv, "qkv", None, 2)
+    _check(a_log, "a_log", torch.float32, 1)
+    _check(dt_bias, "dt_bias", torch.float32, 1)
+    for name, t in (("beta_raw", beta_raw), ("a_raw", a_raw)):
+        if t.dim() != 2 or t.stride(1) != 1 or t.dtype != qkv.dtype or t.shape[0] != qkv.shape[0]:
+            raise KernelError(f"{name} {tuple(t.shape)} does not fit qkv {tuple(qkv.shape)}")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 \
+            or state.shape[1] != heads * dk * dv:
+        raise KernelError(f"state {tuple(state.shape)} does not fit {heads} heads of {dk} x {dv}")
+    if a_log.numel() != heads or dt_bias.numel() != heads * dk or beta_raw.shape[1] < heads \
+            or a_raw.shape[1] < heads * dk or heads % kv_heads or dk > 256:
+        raise KernelError("delta_rule: sizes do not fit (key size at most 256)")
+    T = qkv.shape[0]
+    o = torch.empty((T, heads * dv), dtype=torch.float32, device=qkv.device)
+    f = _fn("delta_rule", "hb_delta_rule",
+            [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+             c_void_p, c_void_p, _LONG, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(o), _p(qkv), qkv.shape[1], offsets[0], offsets[1], offsets[2], _p(beta_raw),
+           beta_raw.stride(0), _p(a_raw), a_raw.stride(0), _p(a_log), _p(dt_bias), _p(state),
+           state.stride(0), _p(ctx.cu_tokens), _p(ctx.slots), ctx.num_seqs, heads, kv_heads, dk, dv,
+           _dt(qkv.dtype), _stream()), "delta_rule")
+    return o
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, heads: int, dv: int,
+                  eps: float) -> torch.Tensor:
+    """o [T, heads * dv] float32 -> per head o / sqrt(mean(o^2) + eps) * weight[dv] *
+    sigmoid(gate), in the dtype of ``gate`` ([T, heads * dv], rows may be strided)."""
+    _check(o, "o", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    if gate.dim() != 2 or gate.stride(1) != 1 or tuple(gate.shape) != tuple(o.shape) \
+            or o.shape[1] != heads * dv or weight.numel() != dv:
+        raise KernelError(f"gated_rmsnorm: o {tuple(o.shape)}, gate {tuple(gate.shape)}, weight "
+                          f"{weight.numel()} do not fit {heads} heads of {dv}")
+    T = o.shape[0]
+    out = torch.empty((T, heads * dv), dtype=gate.dtype, device=o.device)
+    f = _fn("delta_rule", "hb_gated_rmsnorm",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _run(f(_p(out), _p(o), _p(gate), gate.stride(0), _p(weight), T, heads, dv, float(eps),
+           _dt(gate.dtype), _stream()), "gated_rmsnorm")
+    return out
+
+
+# ------------------------------------------------------------------ routed experts
+def moe_topk(logits: torch.Tensor, top: int):
+    """(expert ids int32 [T, top], weights float32 [T, top]): the ``top`` largest sigmoid
+    scores of float32 router ``logits`` [T, experts] (lower index on a tie), largest first."""
+    _check(logits, "logits", torch.float32, 2)
+    T, E = logits.shape
+    if not 0 < top <= min(E, 16):
+        raise KernelError(f"top {top} of {E} experts is not supported (1..16)")
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    f = _fn("moe", "hb_moe_topk", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(ids), _p(weights), _p(logits), T, E, top, _stream()), "moe_topk")
+    return ids, weights
+
+
+def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                w_down: torch.Tensor, limit: float) -> torch.Tensor:
+    """sum over a token's chosen experts of expert(weight * h): ``w_gate_up`` [experts, 2 ff,
+    width] (gate rows, then up rows), ``w_down`` [experts, width, ff], the clamped gate of
+    ``glu_act``.  Returns [T, width] in h's dtype."""
+    _check(h, "h", None, 2)
+    _check(ids, "ids", torch.int32, 2)
+    _check(weights, "weights", torch.float32, 2)
+    _check(w_gate_up, "w_gate_up", h.dtype, 3)
+    _check(w_down, "w_down", h.dtype, 3)
+    T, width = h.shape
+    E, two_ff, w2 = w_gate_up.shape
+    ff = two_ff // 2
+    top = ids.shape[1]
+    if w2 != width or tuple(w_down.shape) != (E, width, ff) or tuple(ids.shape) != (T, top) \
+            or ids.shape != weights.shape:
+        raise KernelError("moe_experts: shapes do not fit")
+    partial = torch.empty((T * top, width), dtype=torch.float32, device=h.device)
+    f = _fn("moe", "hb_moe_expert_rows",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_float, c_int, c_void_p])
+    _run(f(_p(partial), _p(h), _p(w_gate_up), _p(w_down), _p(ids), _p(weights), T, top, width, ff,
+           float(limit), _dt(h.dtype), _stream()), "moe_expert_rows")
+    out = torch.empty((T, width), dtype=h.dtype, device=h.device)
+    f = _fn("moe", "hb_moe_combine", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(partial), T, width, top, _dt(h.dtype), _stream()), "moe_combine")
+    return out

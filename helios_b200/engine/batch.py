@@ -65,6 +65,8 @@ class StepContext:
     block_states: dict = field(default_factory=dict)
     # the norm the block after the running one applies first (None: unknown, or the end)
     norm_after_block: object = None
+    # index of the schedule entry that runs now
+    run_index: int = 0
     extras: dict = field(default_factory=dict)
 
     def part_state(self, part) -> Optional[torch.Tensor]:
@@ -103,7 +105,7 @@ class MetaLayout:
 
 
 def _fill_decode(layout, entries, cache, pad_page, rows_kept, token_ids, positions, seq_of_token, cu,
-                 start, ctx_len, slots, want, tables) -> List[SeqSlice]:
+                 start, ctx_len, slots, want, tables, pad_slot: int = 0) -> List[SeqSlice]:
     """``fill_meta`` for a captured decode step (one token a request, one row a request): whole
     arrays at once instead of slices per request, and a block-table row is written again only
     when its request or that request's table has changed since this buffer was last filled
@@ -135,7 +137,7 @@ def _fill_decode(layout, entries, cache, pad_page, rows_kept, token_ids, positio
     positions[:S] = lengths + [0] * pad
     start[:S] = positions[:S]
     ctx_len[:S] = positions[:S] + 1
-    slots[:S] = slot_of + [0] * pad
+    slots[:S] = slot_of + [pad_slot] * pad
     seq_of_token[:S] = _iota(S)
     want[:S] = seq_of_token[:S]
     cu[:S + 1] = _iota(S + 1)
@@ -164,10 +166,13 @@ def fill_meta(layout: MetaLayout, host: np.ndarray, entries: Sequence[StepEntry]
     v = layout.host_views(host)
     token_ids, positions, seq_of_token, cu, start, ctx_len, slots, want = v[:8]
     tables = [t.reshape(layout.S, w) for t, w in zip(v[8:], layout.widths)]
+    # padding requests keep their fixed-size state in a row of its own, beyond the slots
+    pad_slot = int(getattr(cache, "pad_slot", 0))
     if rows_kept is not None and pad_page is not None and layout.S == layout.T \
             and all(len(e.tokens) == 1 and len(e.want) <= 1 for e in entries):
         return _fill_decode(layout, entries, cache, pad_page, rows_kept,
-                            token_ids, positions, seq_of_token, cu, start, ctx_len, slots, want, tables)
+                            token_ids, positions, seq_of_token, cu, start, ctx_len, slots, want, tables,
+                            pad_slot)
     if rows_kept is not None:
         rows_kept.clear()
     for t in tables:
@@ -207,7 +212,7 @@ def fill_meta(layout: MetaLayout, host: np.ndarray, entries: Sequence[StepEntry]
         token_ids[off:off + n] = 0
         positions[off:off + n] = np.arange(n, dtype=np.int32)
         seq_of_token[off:off + n] = i
-        start[i], ctx_len[i], slots[i] = 0, n, 0
+        start[i], ctx_len[i], slots[i] = 0, n, pad_slot
         want[nw] = off
         nw += 1
         off += n

@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 
 from .. import models as _models  # registers the architectures
-from ..config.registry import resolve_architecture
+from ..config.registry import resolve_architecture, typed_config
 from ..config.model_config import read_config_json
 from ..parts import ModelPlan
 from ..weights import bind_random_weights, load_weights
@@ -52,7 +52,7 @@ class DecoderModel:
         dtype = parse_dtype(dtype)
         cfg_json = read_config_json(Path(model_dir))
         arch = resolve_architecture(cfg_json)
-        plan = arch.build_plan(arch.parse_config(cfg_json))
+        plan = arch.build_plan(typed_config(arch, cfg_json, model_dir))
         load_weights(plan, model_dir, dtype, device)
         return cls(plan, dtype, device)
 
@@ -81,6 +81,7 @@ class DecoderModel:
         runs = len(plan.schedule)
         for entry, run in enumerate(plan.schedule):
             ctx.block_states = cache.part_states(entry)
+            ctx.run_index = entry
             # the norm that meets the residual stream first after this block, if the next
             # block says so: a part may prepare it while it adds its own output
             ctx.norm_after_block = (plan.layers[plan.schedule[entry + 1].layer].first_norm

@@ -26,7 +26,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--max-live", type=int, default=8, help="request slots")
+    ap.add_argument("--max-live", type=int, default=4, help="request slots")
     ap.add_argument("--device", default="cuda:0")
     return ap
 

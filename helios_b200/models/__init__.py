@@ -1,5 +1,6 @@
 """Plan builders; importing this package registers the architectures."""
-from . import dense_decoder
+from . import dense_decoder, zokelix
 from .dense_decoder import build_dense_decoder_plan
+from .zokelix import build_zokelix_plan
 
-__all__ = ["build_dense_decoder_plan", "dense_decoder"]
+__all__ = ["build_dense_decoder_plan", "build_zokelix_plan", "dense_decoder", "zokelix"]

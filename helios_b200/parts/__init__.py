@@ -2,14 +2,19 @@ from .base import (Block, DeferredNorm, FeedForward, InputStage, LayerCache, Mix
                    PositionEncoding, StateSpec, WeightSpec, known_parts, part_class,
                    register_part)
 from .norm import RMSNorm
-from .rotary import RotaryEncoding, rotary_frequencies
+from .rotary import RotaryEncoding, rotary_frequencies, yarn_attention_factor, yarn_frequencies
 from .attention import GQAAttention
-from .mlp import SwiGLU
+from .mlp import GatedMLP, SwiGLU
+from .moe import RoutedExperts
+from .latent_attention import LatentAttention
+from .delta_rule import GatedDeltaMixer
 from .embedding import NormedHead, OutputHead, TokenEmbedding
-from .block import PreNormBlock
+from .block import PostNormBlock, PreNormBlock
 from .plan import ModelPlan, Run
 
 __all__ = ["Block", "DeferredNorm", "FeedForward", "InputStage", "OutputStage", "NormedHead", "LayerCache", "Mixer", "Norm", "PagedCacheSpec", "Part",
            "PositionEncoding", "StateSpec", "WeightSpec", "known_parts", "part_class",
            "register_part", "RMSNorm", "RotaryEncoding", "rotary_frequencies", "GQAAttention",
-           "SwiGLU", "OutputHead", "TokenEmbedding", "PreNormBlock", "ModelPlan", "Run"]
+           "SwiGLU", "OutputHead", "TokenEmbedding", "PreNormBlock", "ModelPlan", "Run",
+           "GatedMLP", "RoutedExperts", "LatentAttention", "GatedDeltaMixer", "PostNormBlock",
+           "yarn_frequencies", "yarn_attention_factor"]

@@ -43,6 +43,7 @@ class PagedCacheSpec:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: every key is needed; W: only the last W
+    planes: int = 2                   # 2: keys and values; 1: one row a token (a latent cache)
 
 
 @dataclass(frozen=True)
@@ -56,7 +57,7 @@ class StateSpec:
 class LayerCache:
     """The pages of one cache id, as a mixer sees them."""
     k_pages: torch.Tensor         # [pages, kv heads, page_size, head_dim]
-    v_pages: torch.Tensor
+    v_pages: Optional[torch.Tensor]   # None where the spec has one plane
     group: int                    # index into StepContext.block_tables
     page_size: int
     write: bool = True            # False: this run reads what another run wrote
@@ -97,6 +98,14 @@ class Norm(Part):
         if delta is not None:
             residual.add_(delta.float())
         return self.forward(residual.to(out_dtype))
+
+    def add_normed(self, residual: torch.Tensor, y: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """``residual += norm(y)`` in float32 and in place, for a block that norms what a
+        sublayer returns; returns the new residual in ``out_dtype`` (the residual itself for
+        float32).  ``y`` None: nothing is added.  The default does it in two steps."""
+        if y is not None:
+            residual.add_(self.forward(y).float())
+        return residual if out_dtype == torch.float32 else residual.to(out_dtype)
 
 
 class PositionEncoding(Part):

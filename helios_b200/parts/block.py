@@ -65,3 +65,61 @@ class PreNormBlock(Block):
 
 
 register_part("block", "pre_norm", PreNormBlock)
+
+
+class PostNormBlock(Block):
+    """x + norm(mixer(x)), then x + norm(feed_forward(x)): the norm sits on a sublayer's
+    OUTPUT, and the sublayers read the residual stream itself (in the activation dtype).
+    The feed-forward, with its norm, may be absent.  The residual sum and the norms are
+    float32; each add is one kernel with its norm, which also leaves the new residual in the
+    activation dtype for the next sublayer (kept for the next block of this kind under the
+    index of the run that made it)."""
+
+    _COPY = "post_norm_block.residual_copy"
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: Optional[FeedForward] = None,
+                 ffn_norm: Optional[Norm] = None,
+                 names: Tuple[str, str, str, str] = ("mix.", "norm1", "mlp.", "norm2")) -> None:
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        self._mixer = mixer
+        self.mixer_norm = mixer_norm
+        self.ffn = ffn
+        self.ffn_norm = ffn_norm
+        self.names = names
+
+    @property
+    def mixer(self) -> Mixer:
+        return self._mixer
+
+    def named_parts(self) -> List[Tuple[str, Part]]:
+        parts = [(self.names[0], self._mixer), (self.names[1], self.mixer_norm)]
+        if self.ffn is not None:
+            parts += [(self.names[2], self.ffn), (self.names[3], self.ffn_norm)]
+        return parts
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for _, p in self.named_parts())
+
+    def forward(self, ctx, residual: torch.Tensor, delta, cache: Optional[LayerCache],
+                state: Optional[torch.Tensor]):
+        if isinstance(delta, DeferredNorm):
+            raise ValueError("a post-norm block takes no deferred norm")
+        kept = ctx.step_tables.pop(self._COPY, None)
+        if delta is not None:
+            residual.add_(delta.float())
+            kept = None
+        if kept is not None and kept[0] == ctx.run_index - 1:
+            h = kept[1]
+        else:
+            h = self.mixer_norm.add_normed(residual, None, ctx.act_dtype) \
+                if ctx.act_dtype != torch.float32 else residual
+        h = self.mixer_norm.add_normed(residual, self._mixer.forward(ctx, h, cache, state), ctx.act_dtype)
+        if self.ffn is not None:
+            h = self.ffn_norm.add_normed(residual, self.ffn.forward(ctx, h), ctx.act_dtype)
+        ctx.step_tables[self._COPY] = (ctx.run_index, h)
+        return residual, None
+
+
+register_part("block", "post_norm", PostNormBlock)

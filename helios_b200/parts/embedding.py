@@ -13,17 +13,18 @@ class TokenEmbedding(InputStage):
     """hidden = table[token ids]; no scale and no position term.  The residual stream
     it starts is float32."""
 
-    def __init__(self, vocab: int, width: int) -> None:
+    def __init__(self, vocab: int, width: int, tensor_name: str = "weight") -> None:
         self.vocab = vocab
         self.vocab_size = vocab
         self.width = width
+        self.tensor_name = tensor_name
         self.table = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.vocab, self.width))}
+        return {self.tensor_name: WeightSpec((self.vocab, self.width))}
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.table = tensors["weight"].contiguous()
+        self.table = tensors[self.tensor_name].contiguous()
 
     def forward(self, ctx) -> torch.Tensor:
         return ops.embedding(ctx.token_ids, self.table)
@@ -32,16 +33,17 @@ class TokenEmbedding(InputStage):
 class OutputHead(Part):
     """logits = rows x W^T, float32, without a bias."""
 
-    def __init__(self, vocab: int, width: int) -> None:
+    def __init__(self, vocab: int, width: int, tensor_name: str = "weight") -> None:
         self.vocab = vocab
         self.width = width
+        self.tensor_name = tensor_name
         self.weight = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.vocab, self.width))}
+        return {self.tensor_name: WeightSpec((self.vocab, self.width))}
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.tensor_name].contiguous()
 
     def kernel_libraries(self, dtype):
         return ops.linear_libraries(dtype)

@@ -70,6 +70,24 @@ def shard_files(model_dir: Path) -> Iterator[Path]:
     yield from shards
 
 
+def tensor_shapes(model_dir) -> Dict[str, Tuple[int, ...]]:
+    """name -> shape of every tensor of the checkpoint, from the files' headers alone."""
+    import struct
+    out: Dict[str, Tuple[int, ...]] = {}
+    try:
+        shards = list(shard_files(Path(model_dir)))
+    except FileNotFoundError:
+        return out
+    for shard in shards:
+        with open(shard, "rb") as f:
+            (n,) = struct.unpack("<Q", f.read(8))
+            header = json.loads(f.read(n))
+        for name, meta in header.items():
+            if name != "__metadata__":
+                out[name] = tuple(int(d) for d in meta["shape"])
+    return out
+
+
 def target_dtype(spec: WeightSpec, compute_dtype: torch.dtype) -> torch.dtype:
     if spec.kind == "matrix":
         return compute_dtype

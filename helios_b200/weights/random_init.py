@@ -71,7 +71,7 @@ def write_model_folder(out_dir, config_json: Dict[str, Any], seed: int,
     with open(out / "config.json", "w", encoding="utf-8") as f:
         json.dump(config_json, f, indent=2)
     if tokenizer:
-        write_byte_tokenizer(out, int(config_json["vocab_size"]))
+        write_byte_tokenizer(out, int(plan.vocab_size))
     return out
 
 
