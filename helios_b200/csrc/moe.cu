@@ -1,7 +1,8 @@
 // Routed feed-forward: every token runs `top` of `experts` small gated feed-forward layers.
 //
 //   z = W_router h (float32), s = sigmoid(z); the `top` experts with the largest s are
-//   chosen (the lower index on a tie); an expert's weight is its s, not renormalised, and
+//   chosen (compared by z, which orders them as s does without saturating; the lower index
+//   on a tie); an expert's weight is its s, not renormalised, and
 //   multiplies the expert's INPUT:  out = sum over chosen e of expert_e(s_e * h).
 //
 // `moe_topk` picks experts and weights.  `moe_expert_rows` runs one (token, choice) pair per
@@ -23,19 +24,17 @@ __global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weigh
   const float* z = logits + (size_t)t * experts;
   int chosen[MOE_MAX_TOP];
   for (int k = 0; k < top; ++k) {
-    float best = -1.f;
-    int at = 0;
-    bool found = false;
+    float best = 0.f;
+    int at = -1;
     for (int e = 0; e < experts; ++e) {
       bool taken = false;
       for (int j = 0; j < k; ++j) taken |= (chosen[j] == e);
       if (taken) continue;
-      const float s = 1.f / (1.f + expf(-z[e]));
-      if (!found || s > best) { best = s; at = e; found = true; }
+      if (at < 0 || z[e] > best) { best = z[e]; at = e; }     // a NaN never wins: `at` stays valid
     }
     chosen[k] = at;
     ids[(size_t)t * top + k] = at;
-    weights[(size_t)t * top + k] = best;
+    weights[(size_t)t * top + k] = 1.f / (1.f + expf(-best));
   }
 }
 

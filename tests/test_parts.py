@@ -363,7 +363,7 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
             model = DecoderModel.from_config(cfg_json, seed=4, dtype=dtype)
             assert not model.plan.graph_safe
             core = EngineCore(model, page_size=8, num_pages=32, max_slots=2)
-            assert list(core.cache.states) == [1] and core.cache.states[1].shape == (2, 65)
+            assert list(core.cache.states) == [1] and core.cache.states[1].shape == (3, 65)   # two slots and the padding requests' row
             assert len(core.cache._where) == 2               # only the attention layers have pages
             a, b = random_tokens(256, 23, 1), random_tokens(256, 9, 2)
             whole_a = core.step([StepEntry("a", a, list(range(23)))]).clone()
