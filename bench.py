@@ -310,6 +310,166 @@ def run_reference(args):
     return 0
 
 
+# ---------------------------------------------------------------------- another design beside the dense decoder
+def design_configs(size):
+    """(Zokelix config.json, dense decoder config.json of equal width, head count, layers, vocabulary
+    and active feed-forward size) at layer sizes of a real model.  Six layers: attention over a
+    latent cache and the gated-delta-rule mixer in the order L D L L D L, the first feed-forward
+    dense, the others routed."""
+    if size == "large":
+        width, heads, hd, rank, ff, experts, top, eff, vocab = 2048, 16, 128, 512, 8192, 32, 4, 2048, 32000
+    else:
+        width, heads, hd, rank, ff, experts, top, eff, vocab = 1024, 8, 64, 256, 4096, 16, 2, 2048, 32000
+    rot = {"base": 500000.0, "dims": hd // 2, "scaling": {"factor": 8.0, "fast": 32.0, "slow": 1.0, "original": 4096}}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": heads, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": rank,
+                        "scale": (hd + hd // 2) ** -0.5, "rot": rot}}
+    delta = {"type": "channel_delta",
+             "mixer": {"heads": heads, "kv_heads": heads, "dim": hd, "vdim": hd, "conv": 4, "low_rank": 64}}
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": experts, "top": top}}
+    layers = []
+    for i, kind in enumerate("LDLLDL"):
+        layer = dict(latent if kind == "L" else delta)
+        layer["mlp"] = {"kind": "dense", "ff": ff} if i == 0 else moe
+        layers.append(layer)
+    zk = {"architecture": "Zokelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": layers}
+    dense = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": vocab,
+             "hidden_size": width, "intermediate_size": top * eff, "num_hidden_layers": 6,
+             "num_attention_heads": heads, "num_key_value_heads": max(1, heads // 4), "head_dim": hd,
+             "max_position_embeddings": 32768, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+             "attention_bias": False, "tie_word_embeddings": False, "hidden_act": "silu",
+             "torch_dtype": "bfloat16"}
+    return zk, dense
+
+
+def run_design(args):
+    """``--design zokelix``: prefill and decode throughput of the design at two size sets beside a
+    dense decoder of equal size, and where a step's time goes, op by op (CUDA events around every
+    launcher of ``ops``, steps run kernel by kernel for that table only)."""
+    import torch
+    from helios_b200.csrc import ops
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(args.seed)
+    page, ctx_end, prompt = 16, args.context, PREFILL_TOKENS
+    out = {"design": args.design, "context": ctx_end, "prefill_tokens": prompt, "sizes": {}}
+
+    def timed(fn, n):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        torch.cuda.synchronize()
+        marks[0].record()
+        for _ in range(n):
+            fn()
+        marks[1].record()
+        torch.cuda.synchronize()
+        return marks[0].elapsed_time(marks[1]) / n
+
+    OPS = ["linear", "linear_bf16", "linear_logits", "linear_swiglu", "add_rmsnorm", "rmsnorm_add", "glu_act",
+           "embedding", "rotary_table", "attention", "latent_prepare", "head_gemm", "latent_attention",
+           "causal_conv_silu", "delta_rule", "gated_rmsnorm", "moe_topk", "moe_experts"]
+
+    def op_table(core, entries_fn, reps=3):
+        """milliseconds per op name over one step, run kernel by kernel (nested ops count inside
+        their caller only)."""
+        spans, depth, saved = [], [0], {}
+        for name in OPS:
+            fn = saved[name] = getattr(ops, name)
+
+            def wrapped(*a, _fn=fn, _name=name, **kw):
+                if depth[0]:
+                    return _fn(*a, **kw)
+                depth[0] += 1
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                try:
+                    return _fn(*a, **kw)
+                finally:
+                    e1.record()
+                    spans.append((_name, e0, e1))
+                    depth[0] -= 1
+            setattr(ops, name, wrapped)
+        graphs, core.use_cuda_graphs = core.use_cuda_graphs, False
+        try:
+            for r in range(reps):
+                spans.clear()
+                core.step(entries_fn())
+                torch.cuda.synchronize()
+                for rid in {e.request_id for e in entries_fn.last}:
+                    if rid.startswith("t"):
+                        core.end(rid)
+        finally:
+            core.use_cuda_graphs = graphs
+            for name, fn in saved.items():
+                setattr(ops, name, fn)
+        table = {}
+        for name, e0, e1 in spans:
+            table[name] = table.get(name, 0.0) + e0.elapsed_time(e1)
+        return {k: round(v, 4) for k, v in sorted(table.items(), key=lambda kv: -kv[1])}
+
+    for size in [s for s in args.design_sizes.split(",") if s]:
+        zk, dense = design_configs(size)
+        res = {}
+        for label, cfg in (("zokelix", zk), ("dense", dense)):
+            vocab = cfg.get("vocab") or cfg["vocab_size"]
+            model = DecoderModel.from_config(cfg, seed=args.seed, dtype="bfloat16", device=dev)
+            batches = [int(b) for b in args.design_batches.split(",")]
+            core = EngineCore(model, page_size=page, num_pages=max(batches) * (ctx_end // page + 1) + 2 * prompt // page,
+                              max_slots=max(batches) + 1, max_model_len=max(ctx_end, prompt) + 8)
+            r = {}
+            # prefill: one prompt of 2,048 tokens, the shape's captured graph once it exists
+            times = []
+            runs = EngineCore.FULL_GRAPH_EAGER_RUNS + 5
+            for i in range(runs):
+                toks = torch.randint(0, vocab, (prompt,), generator=gen).tolist()
+                ms = timed(lambda: core.step([StepEntry("p", toks, [prompt - 1])]), 1)
+                core.end("p")
+                if i >= runs - 3:
+                    times.append(ms)
+            r["prefill_ms"] = round(statistics.median(times), 3)
+            r["prefill_tokens_per_s"] = round(prompt / statistics.median(times) * 1e3, 1)
+
+            def prefill_entries():
+                prefill_entries.last = [StepEntry("t0", torch.randint(0, vocab, (prompt,), generator=gen).tolist(), [prompt - 1])]
+                return prefill_entries.last
+            r["prefill_ops_ms"] = op_table(core, prefill_entries)
+            # decode at context ctx_end
+            for batch in batches:
+                steps, warm = args.steps, args.warmup
+                ctx0 = ctx_end - steps - warm - 8
+                for b in range(batch):
+                    left = ctx0
+                    while left > 0:
+                        n = min(left, prompt)
+                        core.step([StepEntry(f"d{b}", torch.randint(0, vocab, (n,), generator=gen).tolist(), [])])
+                        left -= n
+                last = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+
+                def one():
+                    core.step([StepEntry(f"d{b}", [last[b]], [0]) for b in range(batch)])
+                for _ in range(8 + warm):
+                    one()
+                ms = timed(one, steps)
+                r[f"decode_b{batch}_ms"] = round(ms, 4)
+                r[f"decode_b{batch}_tokens_per_s"] = round(batch / ms * 1e3, 1)
+
+                def decode_entries():
+                    decode_entries.last = [StepEntry(f"d{b}", [last[b]], [0]) for b in range(batch)]
+                    return decode_entries.last
+                r[f"decode_b{batch}_ops_ms"] = op_table(core, decode_entries)
+                for b in range(batch):
+                    core.end(f"d{b}")
+            res[label] = r
+            del core, model
+            torch.cuda.empty_cache()
+        out["sizes"][size] = res
+    print(json.dumps(out))
+    return 0
+
+
 def mixed_prompts(args, vocab, gen):
     """BASELINE config 4's workload: prompt lengths uniform in [min, max], ids uniform."""
     import torch
@@ -508,6 +668,11 @@ def main():
     ap.add_argument("--max-prompt", type=int, default=4096)
     ap.add_argument("--budget", type=int, default=2048, help="tokens a step (chunked prefill)")
     ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--design", default=None, choices=["zokelix"],
+                    help="measure another design of the package beside a dense decoder of equal size "
+                         "(prefill, decode, time by op) instead of the default workload")
+    ap.add_argument("--design-sizes", default="small,large")
+    ap.add_argument("--design-batches", default="8,64")
     ap.add_argument("--micro", default=None, choices=["gemm", "attention_decode", "sampling"],
                     help="time one kind of kernel as a chain in a captured graph instead of the step "
                          "(sizes of --model; --batch tokens or requests, --context keys)")
@@ -523,6 +688,9 @@ def main():
         return run_reference(args)
     if args.micro:
         return run_micro(args)
+    if args.design:
+        args.warmup = max(3, args.warmup)
+        return run_design(args)
     if args.warmup < 3:
         args.warmup = 3
 

@@ -257,3 +257,279 @@ HB_EXPORT int hb_latent_attention(void* out, const void* q_lat, long ql_t, long 
               rank, rot, page_size, scale));
   return hb_check_launch();
 }
+
+// ---------------------------------------------------------------- attention on the tensor cores
+// bfloat16, rank a multiple of 32 (at most 512), rot a multiple of 16.  All heads of all tokens
+// of a request attend the same rows, so a block takes 32 query rows = (token, head) pairs of
+// one request (`tokens_per_tile` tokens x `heads_per_block` heads) against tiles of 32 keys:
+//
+//   8 warps = 2 row groups of 16 rows x 4 column quarters.  Scores: warp (rg, cq) computes
+//   the 16 x 8 block of its row group against keys 8 cq .. 8 cq + 7 (mma.sync m16n8k16 over
+//   rank + rot), masks by position and leaves it in shared memory.  After a barrier every
+//   warp of the row group reads the 16 x 32 scores, does the online-softmax step (float32,
+//   base 2) and adds P V for its quarter of the latent's columns: V is the first `rank`
+//   values of the very rows that were the keys, already in shared memory.
+//
+// Key tiles arrive by 16-byte cp.async, one tile ahead.  The keys of a request are cut into
+// `n_splits` ranges (blockIdx.z), so that steps of few rows still fill the SMs; with more
+// than one range the blocks leave unnormalised sums, maxima and weights, and
+// `latent_attention_merge` puts them together.
+#include "attention_mma.cuh"
+
+constexpr int LM_ROWS = 32, LM_KEYS = 32, LM_MAXNT = 16, LM_SPAD = 36;
+
+__global__ void __launch_bounds__(256)
+latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_acc,
+                            float* __restrict__ part_ml,
+                            const __nv_bfloat16* __restrict__ q_lat, long ql_t, long ql_h,
+                            const __nv_bfloat16* __restrict__ q_rot, long qr_t, long qr_h,
+                            const __nv_bfloat16* __restrict__ pages,
+                            const int* __restrict__ block_table, int bt_stride,
+                            const int* __restrict__ q_tiles, const int* __restrict__ cu_tokens,
+                            const int* __restrict__ start_pos, int heads, int heads_per_block,
+                            int tokens_per_tile, int rank, int rot, int page_size,
+                            float scale_log2, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char lm_smem[];
+  const int D = rank + rot, RS = D + 8;
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);      // [32][RS]
+  __nv_bfloat16* k_s = q_s + LM_ROWS * RS;                             // [2][32][RS]
+  float* s_s = reinterpret_cast<float*>(k_s + 2 * LM_KEYS * RS);       // [32][LM_SPAD]
+  int* row_pos = reinterpret_cast<int*>(s_s + LM_ROWS * LM_SPAD);      // [32]
+  int* row_out = row_pos + LM_ROWS;                                    // [32]: token * heads + head, -1 for none
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rg = warp >> 2, cq = warp & 3, g = lane >> 2, t4 = lane & 3;
+  const int seq = q_tiles[2 * blockIdx.x], t_first = q_tiles[2 * blockIdx.x + 1];
+  const int tok0 = cu_tokens[seq], n_tok = cu_tokens[seq + 1] - tok0;
+  if (t_first >= n_tok) return;                       // a tile that holds no work
+  const int h0 = blockIdx.y * heads_per_block;
+  const int split = blockIdx.z;
+  const int* table = block_table + (size_t)seq * bt_stride;
+  const int last_tok = min(t_first + tokens_per_tile, n_tok);
+  const int n_keys = start_pos[seq] + last_tok;       // the tile's last token sees this many keys
+  const int n_kt = (n_keys + LM_KEYS - 1) / LM_KEYS;
+  const int per = (n_kt + n_splits - 1) / n_splits;
+  const int kt_lo = split * per, kt_hi = min(n_kt, kt_lo + per);
+
+  if (tid < LM_ROWS) {
+    const int lt = tid / heads_per_block, h = h0 + tid % heads_per_block;
+    const bool ok = lt < tokens_per_tile && t_first + lt < n_tok && h < heads;
+    row_pos[tid] = ok ? start_pos[seq] + t_first + lt : -1;
+    row_out[tid] = ok ? (tok0 + t_first + lt) * heads + h : -1;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < LM_ROWS * D; idx += 256) {
+    const int r = idx / D, d = idx - r * D;
+    __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+    if (row_out[r] >= 0) {
+      const int tg = row_out[r] / heads, h = row_out[r] - tg * heads;
+      v = d < rank ? q_lat[(size_t)tg * ql_t + (size_t)h * ql_h + d]
+                   : q_rot[(size_t)tg * qr_t + (size_t)h * qr_h + (d - rank)];
+    }
+    q_s[r * RS + d] = v;
+  }
+
+  const int vec_per_row = D / 8;
+  auto load_tile = [&](int kt, int buf) {
+    __nv_bfloat16* dst = k_s + (size_t)buf * LM_KEYS * RS;
+    for (int idx = tid; idx < LM_KEYS * vec_per_row; idx += 256) {
+      const int r = idx / vec_per_row, v = idx - r * vec_per_row;
+      const int key = kt * LM_KEYS + r;
+      const bool ok = key < n_keys;
+      const __nv_bfloat16* src = pages;
+      if (ok) src = pages + ((size_t)table[key / page_size] * page_size + key % page_size) * D + v * 8;
+      cp_async16(dst + r * RS + v * 8, src, ok ? 16 : 0);
+    }
+  };
+
+  float acc[LM_MAXNT][4];
+#pragma unroll
+  for (int i = 0; i < LM_MAXNT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int ntq = rank / 32;                          // 8-column tiles of this warp's quarter
+  const int col_q = cq * (rank / 4);
+  const int ksteps = D / 16;
+
+  if (kt_lo < kt_hi) load_tile(kt_lo, 0);
+  cp_async_commit();
+  int buf = 0;
+  for (int kt = kt_lo; kt < kt_hi; ++kt) {
+    cp_async_wait<0>();
+    __syncthreads();
+    if (kt + 1 < kt_hi) load_tile(kt + 1, buf ^ 1);
+    cp_async_commit();
+    const __nv_bfloat16* kt_s = k_s + (size_t)buf * LM_KEYS * RS;
+    // scores of 16 rows against 8 keys
+    {
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      const __nv_bfloat16* krow = kt_s + (8 * cq + g) * RS + 2 * t4;
+      const __nv_bfloat16* qbase = q_s + (rg * 16 + (lane & 15)) * RS + (lane >> 4) * 8;
+      for (int ks = 0; ks < ksteps; ++ks) {
+        uint32_t a[4];
+        ldmatrix_x4(a, qbase + ks * 16);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
+        mma_bf16(c, a, b0, b1);
+      }
+      const int key = kt * LM_KEYS + 8 * cq + 2 * t4;
+      const int ra = rg * 16 + g, rb = ra + 8;
+      const int pa = row_pos[ra], pb = row_pos[rb];
+      s_s[ra * LM_SPAD + 8 * cq + 2 * t4] = key <= pa ? c[0] * scale_log2 : -INFINITY;
+      s_s[ra * LM_SPAD + 8 * cq + 2 * t4 + 1] = key + 1 <= pa ? c[1] * scale_log2 : -INFINITY;
+      s_s[rb * LM_SPAD + 8 * cq + 2 * t4] = key <= pb ? c[2] * scale_log2 : -INFINITY;
+      s_s[rb * LM_SPAD + 8 * cq + 2 * t4 + 1] = key + 1 <= pb ? c[3] * scale_log2 : -INFINITY;
+    }
+    __syncthreads();
+    // online softmax over the row group's 16 x 32 scores, then P V for this warp's columns
+    uint32_t pfrag[2][4];
+    {
+      float p[2][8];
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const float* srow = s_s + (rg * 16 + g + 8 * r) * LM_SPAD + 2 * t4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          p[r][2 * j] = srow[8 * j];
+          p[r][2 * j + 1] = srow[8 * j + 1];
+          mx[r] = fmaxf(mx[r], fmaxf(p[r][2 * j], p[r][2 * j + 1]));
+        }
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float corr = exp2f(m[r] - m_use);
+        m[r] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          p[r][j] = exp2f(p[r][j] - m_use);
+          sum += p[r][j];
+        }
+        l[r] = l[r] * corr + sum;
+#pragma unroll
+        for (int nt = 0; nt < LM_MAXNT; ++nt)
+          if (nt < ntq) {
+            acc[nt][2 * r] *= corr;
+            acc[nt][2 * r + 1] *= corr;
+          }
+      }
+      // columns 2 t4 + 8 j of the 32 keys: j = 0, 1 belong to keys 0..15, j = 2, 3 to 16..31
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        pfrag[kk][0] = pack_bf16(p[0][4 * kk], p[0][4 * kk + 1]);
+        pfrag[kk][1] = pack_bf16(p[1][4 * kk], p[1][4 * kk + 1]);
+        pfrag[kk][2] = pack_bf16(p[0][4 * kk + 2], p[0][4 * kk + 3]);
+        pfrag[kk][3] = pack_bf16(p[1][4 * kk + 2], p[1][4 * kk + 3]);
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      const __nv_bfloat16* vbase = kt_s + (16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7)) * RS + col_q + (lane >> 4) * 8;
+#pragma unroll
+      for (int dp = 0; dp < LM_MAXNT / 2; ++dp)
+        if (2 * dp < ntq) {
+          uint32_t r4[4];
+          ldmatrix_x4_trans(r4, vbase + 16 * dp);
+          mma_bf16(acc[2 * dp], pfrag[kk], r4[0], r4[1]);
+          if (2 * dp + 1 < ntq) mma_bf16(acc[2 * dp + 1], pfrag[kk], r4[2], r4[3]);
+        }
+    }
+    buf ^= 1;
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = row_out[rg * 16 + g + 8 * r];
+    if (row < 0) continue;
+    if (n_splits == 1) {
+      const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+      __nv_bfloat16* dst = out + (size_t)row * rank + col_q + 2 * t4;
+#pragma unroll
+      for (int nt = 0; nt < LM_MAXNT; ++nt)
+        if (nt < ntq)
+          *reinterpret_cast<__nv_bfloat162*>(dst + 8 * nt) =
+              __floats2bfloat162_rn(acc[nt][2 * r] * inv, acc[nt][2 * r + 1] * inv);
+    } else {
+      float* dst = part_acc + ((size_t)row * n_splits + split) * rank + col_q + 2 * t4;
+#pragma unroll
+      for (int nt = 0; nt < LM_MAXNT; ++nt)
+        if (nt < ntq) *reinterpret_cast<float2*>(dst + 8 * nt) = make_float2(acc[nt][2 * r], acc[nt][2 * r + 1]);
+      if (cq == 0 && t4 == 0) {
+        part_ml[((size_t)row * n_splits + split) * 2] = m[r];
+        part_ml[((size_t)row * n_splits + split) * 2 + 1] = l[r];
+      }
+    }
+  }
+}
+
+// out[row] = sum_i 2^(m_i - M) acc_i / sum_i 2^(m_i - M) l_i over the ranges, i in order
+__global__ void latent_attention_merge_kernel(__nv_bfloat16* __restrict__ out,
+                                              const float* __restrict__ part_acc,
+                                              const float* __restrict__ part_ml, int n_rows,
+                                              int rank, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  const float* ml = part_ml + (size_t)row * n_splits * 2;
+  float M = -INFINITY;
+  for (int i = 0; i < n_splits; ++i) M = fmaxf(M, ml[2 * i]);
+  float L = 0.f;
+  for (int i = 0; i < n_splits; ++i) L += (ml[2 * i] == -INFINITY ? 0.f : exp2f(ml[2 * i] - M)) * ml[2 * i + 1];
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int d = lane; d < rank; d += 32) {
+    float a = 0.f;
+    for (int i = 0; i < n_splits; ++i) {
+      const float w = ml[2 * i] == -INFINITY ? 0.f : exp2f(ml[2 * i] - M);
+      a = fmaf(w, part_acc[((size_t)row * n_splits + i) * rank + d], a);
+    }
+    out[(size_t)row * rank + d] = __float2bfloat16_rn(a * inv);
+  }
+}
+
+HB_EXPORT int hb_latent_attention_mma(void* out, float* part_acc, float* part_ml, const void* q_lat,
+                                      long ql_t, long ql_h, const void* q_rot, long qr_t, long qr_h,
+                                      const void* pages, const int* block_table, int bt_stride,
+                                      const int* q_tiles, int n_tiles, const int* cu_tokens,
+                                      const int* start_pos, int n_tokens, int heads,
+                                      int heads_per_block, int tokens_per_tile, int rank, int rot,
+                                      int page_size, float scale, int n_splits, cudaStream_t stream) {
+  if (n_tiles <= 0 || n_tokens <= 0) return HB_OK;
+  if (rank <= 0 || rank % 32 || rank > 32 * LM_MAXNT || rot < 0 || rot % 16 || heads <= 0 ||
+      heads_per_block <= 0 || heads_per_block > LM_ROWS || tokens_per_tile <= 0 ||
+      tokens_per_tile * heads_per_block > LM_ROWS || page_size <= 0 || n_splits <= 0 ||
+      n_splits > 65535 || (n_splits > 1 && (part_acc == nullptr || part_ml == nullptr)))
+    return HB_BAD_ARGUMENT;
+  const int RS = rank + rot + 8;
+  const size_t smem = (size_t)3 * LM_ROWS * RS * 2 + (size_t)LM_ROWS * LM_SPAD * 4 + 2 * LM_ROWS * 4;
+  if (smem > 220 * 1024) return HB_BAD_ARGUMENT;
+  static size_t smem_set = 0;
+  if (smem > 48 * 1024 && smem > smem_set) {
+    if (cudaFuncSetAttribute(latent_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return HB_LAUNCH_FAILED;
+    smem_set = smem;
+  }
+  const int head_groups = (heads + heads_per_block - 1) / heads_per_block;
+  hb_launch(latent_attention_mma_kernel, dim3(n_tiles, head_groups, n_splits), dim3(256), smem, stream,
+            (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q_lat, ql_t, ql_h,
+            (const __nv_bfloat16*)q_rot, qr_t, qr_h, (const __nv_bfloat16*)pages, block_table, bt_stride,
+            q_tiles, cu_tokens, start_pos, heads, heads_per_block, tokens_per_tile, rank, rot, page_size,
+            scale * 1.4426950408889634f, n_splits);
+  if (n_splits > 1) {
+    const int n_rows = n_tokens * heads;
+    hb_launch(latent_attention_merge_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream,
+              (__nv_bfloat16*)out, (const float*)part_acc, (const float*)part_ml, n_rows, rank, n_splits);
+  }
+  return hb_check_launch();
+}

@@ -144,3 +144,88 @@ HB_EXPORT int hb_moe_combine(void* out, const float* partial, int n_tokens, int 
               partial, total, width, top));
   return hb_check_launch();
 }
+
+// ---------------------------------------------------------------- steps of many tokens
+// The (token, choice) pairs are put in the order of their experts, so that every expert's
+// rows are one contiguous run and the two products of all experts are one grouped matrix
+// product each.  `moe_sort`: ends[e] = number of pairs of experts 0..e (the run of expert e
+// is [ends[e-1], ends[e])), place[pair] = the pair's row in that order.  One block; the
+// order inside a run is whatever the atomics give, which no result depends on: a row's
+// product is the same wherever it lies.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(int* __restrict__ ends, int* __restrict__ place, const int* __restrict__ ids,
+                int n_pairs, int experts) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ int cursor[];          // [experts]
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) cursor[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&cursor[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int c = cursor[e];
+      cursor[e] = run;
+      run += c;
+      ends[e] = run;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) place[i] = atomicAdd(&cursor[ids[i]], 1);
+}
+
+HB_EXPORT int hb_moe_sort(int* ends, int* place, const int* ids, int n_pairs, int experts,
+                          cudaStream_t stream) {
+  if (n_pairs <= 0) return HB_OK;
+  if (experts <= 0 || experts > 8192) return HB_BAD_ARGUMENT;
+  hb_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)experts * sizeof(int), stream, ends, place,
+            ids, n_pairs, experts);
+  return hb_check_launch();
+}
+
+// rows[place[pair], :] = weight[pair] * h[pair / top, :], rounded to the activation dtype
+template <typename T>
+__global__ void moe_scatter_rows_kernel(T* __restrict__ rows, const T* __restrict__ h,
+                                        const int* __restrict__ place,
+                                        const float* __restrict__ weights, int top, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  const float w = weights[pair];
+  const T* src = h + (size_t)(pair / top) * width;
+  T* dst = rows + (size_t)place[pair] * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = from_float<T>(w * to_float(src[c]));
+}
+
+HB_EXPORT int hb_moe_scatter_rows(void* rows, const void* h, const int* place, const float* weights,
+                                  int n_tokens, int top, int width, int act_dt, cudaStream_t stream) {
+  if (n_tokens <= 0) return HB_OK;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(moe_scatter_rows_kernel<TA>, dim3(n_tokens * top), dim3(256), 0, stream, (TA*)rows,
+              (const TA*)h, place, weights, top, width));
+  return hb_check_launch();
+}
+
+// out[t, :] = sum over k = 0..top-1, in that order, of rows[place[t * top + k], :]
+template <typename T>
+__global__ void moe_gather_sum_kernel(T* __restrict__ out, const T* __restrict__ rows,
+                                      const int* __restrict__ place, int top, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) a += to_float(rows[(size_t)place[t * top + k] * width + c]);
+    out[(size_t)t * width + c] = from_float<T>(a);
+  }
+}
+
+HB_EXPORT int hb_moe_gather_sum(void* out, const void* rows, const int* place, int n_tokens, int top,
+                                int width, int act_dt, cudaStream_t stream) {
+  if (n_tokens <= 0) return HB_OK;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(moe_gather_sum_kernel<TA>, dim3(n_tokens), dim3(256), 0, stream, (TA*)out,
+              (const TA*)rows, place, top, width));
+  return hb_check_launch();
+}

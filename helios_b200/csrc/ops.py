@@ -1174,13 +1174,20 @@ def head_gemm(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+#: bfloat16 steps run attention over the latent cache on the tensor cores where the sizes
+#: allow (rank a multiple of 32, rotated part a multiple of 16); float32 and other sizes run
+#: the kernel with one warp a row, whose sums have a fixed order
+LATENT_ATTENTION_TENSOR_CORES = True
+
+
 def latent_attention(ctx, q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tensor,
                      block_table: torch.Tensor, rank: int, rot: int, page_size: int,
                      scale: float) -> torch.Tensor:
     """Causal attention of every token of the step over its request's latent rows.  ``q_lat``
     [T, heads, rank] and ``q_rot`` [T, heads, rot] are views with a contiguous last dimension;
     ``pages`` [pages, 1, page_size, rank + rot].  Returns [T, heads, rank] (softmax-weighted
-    sums of the rows' first ``rank`` values)."""
+    sums of the rows' first ``rank`` values).  ``ctx`` gives seq_of_token and positions, and
+    for the tensor-core kernel cu_tokens, start_pos, seqs, max_context_len and extras."""
     _check(pages, "pages", q_lat.dtype, 4)
     _check(block_table, "block_table", torch.int32, 2)
     if q_lat.dim() != 3 or q_rot.dim() != 3 or q_lat.stride(2) != 1 or q_rot.stride(2) != 1 \
@@ -1194,6 +1201,28 @@ def latent_attention(ctx, q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch
         raise KernelError(f"latent rank {rank} (at most 512) or row {rank + rot} (at most 1024) is not supported")
     T, H = q_lat.shape[:2]
     out = torch.empty((T, H, rank), dtype=q_lat.dtype, device=q_lat.device)
+    if LATENT_ATTENTION_TENSOR_CORES and q_lat.dtype == torch.bfloat16 and rank % 32 == 0 and rot % 16 == 0:
+        # 32 query rows a block: (token, head) pairs of one request, which share every key
+        hpb = min(H, 32)
+        tpt = max(1, 32 // hpb)
+        tiles = _step_tiles(ctx, tpt, False, q_lat.device)
+        blocks = tiles.shape[0] * -(-H // hpb)
+        n_splits = 1
+        if blocks < sm_count():
+            n_splits = max(1, min(32, ctx.max_context_len // 256, -(-2 * sm_count() // blocks)))
+        part_acc = part_ml = None
+        if n_splits > 1:
+            part_acc = torch.empty((T * H, n_splits, rank), dtype=torch.float32, device=q_lat.device)
+            part_ml = torch.empty((T * H, n_splits, 2), dtype=torch.float32, device=q_lat.device)
+        f = _fn("latent_attention", "hb_latent_attention_mma",
+                [c_void_p, c_void_p, c_void_p, c_void_p, _LONG, _LONG, c_void_p, _LONG, _LONG, c_void_p,
+                 c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                 c_int, c_int, c_float, c_int, c_void_p])
+        _run(f(_p(out), _p(part_acc), _p(part_ml), _p(q_lat), q_lat.stride(0), q_lat.stride(1), _p(q_rot),
+               q_rot.stride(0), q_rot.stride(1), _p(pages), _p(block_table), block_table.shape[1],
+               _p(tiles), tiles.shape[0], _p(ctx.cu_tokens), _p(ctx.start_pos), T, H, hpb, tpt, rank, rot,
+               page_size, float(scale), n_splits, _stream()), "latent_attention_mma")
+        return out
     f = _fn("latent_attention", "hb_latent_attention",
             [c_void_p, c_void_p, _LONG, _LONG, c_void_p, _LONG, _LONG, c_void_p, c_void_p, c_int, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
@@ -1298,6 +1327,39 @@ def moe_topk(logits: torch.Tensor, top: int):
     return ids, weights
 
 
+#: bfloat16 steps of more than this many tokens run the experts as two grouped matrix products
+#: of the library (tensor cores; rows sorted by expert on the device, no host round trip, so
+#: the step stays capturable); up to it, and in float32, every (token, choice) pair streams its
+#: expert's rows once, which is what a step of few tokens is bound by
+MOE_GROUPED_MIN_TOKENS = 1
+
+
+def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                        w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float) -> torch.Tensor:
+    """``moe_experts`` for many tokens: sort the pairs by expert, scale and scatter the rows,
+    one grouped product for gate|up, the gate, one for down, and a gather that adds a token's
+    choices in their order."""
+    T, width = h.shape
+    E, two_ff, _ = w_gate_up.shape
+    top = ids.shape[1]
+    pairs = T * top
+    ends = torch.empty((E,), dtype=torch.int32, device=h.device)
+    place = torch.empty((pairs,), dtype=torch.int32, device=h.device)
+    f = _fn("moe", "hb_moe_sort", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _run(f(_p(ends), _p(place), _p(ids), pairs, E, _stream()), "moe_sort")
+    rows = torch.empty((pairs, width), dtype=h.dtype, device=h.device)
+    f = _fn("moe", "hb_moe_scatter_rows",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(rows), _p(h), _p(place), _p(weights), T, top, width, _dt(h.dtype), _stream()), "moe_scatter_rows")
+    gate_up = torch._grouped_mm(rows, w_gate_up.transpose(1, 2), offs=ends)
+    y = glu_act(gate_up, "clamped_swish", limit)
+    down = torch._grouped_mm(y, w_down.transpose(1, 2), offs=ends)
+    out = torch.empty((T, width), dtype=h.dtype, device=h.device)
+    f = _fn("moe", "hb_moe_gather_sum", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(down), _p(place), T, top, width, _dt(h.dtype), _stream()), "moe_gather_sum")
+    return out
+
+
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, limit: float) -> torch.Tensor:
     """sum over a token's chosen experts of expert(weight * h): ``w_gate_up`` [experts, 2 ff,
@@ -1315,6 +1377,9 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     if w2 != width or tuple(w_down.shape) != (E, width, ff) or tuple(ids.shape) != (T, top) \
             or ids.shape != weights.shape:
         raise KernelError("moe_experts: shapes do not fit")
+    if h.dtype == torch.bfloat16 and T >= MOE_GROUPED_MIN_TOKENS and width % 8 == 0 and ff % 8 == 0 \
+            and hasattr(torch, "_grouped_mm"):
+        return moe_experts_grouped(h, ids, weights, w_gate_up, w_down, limit)
     partial = torch.empty((T * top, width), dtype=torch.float32, device=h.device)
     f = _fn("moe", "hb_moe_expert_rows",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,

@@ -300,7 +300,7 @@ def test_latent_attention_kernel_far_key_page_borders_and_first_tokens(dtype):
     dt = torch.float32 if dtype == "float32" else torch.bfloat16
     dev = "cuda"
     g = torch.Generator().manual_seed(3)
-    n, page, rank, rot, heads = 300, 16, 40, 8, 3
+    n, page, rank, rot, heads = 300, 16, (40 if dtype == "float32" else 64), (8 if dtype == "float32" else 16), 3
     rows = torch.randn(n, rank + rot, generator=g)
     rows = (rows / rows.norm(dim=-1, keepdim=True)).to(dt).float()
     n_pages = -(-n // page)
@@ -316,9 +316,13 @@ def test_latent_attention_kernel_far_key_page_borders_and_first_tokens(dtype):
         for h in range(heads):
             q[i, h] = rows[key] * (40.0 + 10 * h)         # score 40..60 at the chosen key, |.| < that elsewhere
     q = q.to(dt)
-    ctx = SimpleNamespace(seq_of_token=torch.zeros(len(cases), dtype=torch.int32, device=dev),
-                          positions=q_pos.to(dev))
-    table = order.to(torch.int32).view(1, -1).contiguous().to(dev)
+    from helios_b200.engine.batch import SeqSlice
+    # every query is a request of its own with one token, all reading the same pages
+    ctx = SimpleNamespace(seq_of_token=torch.arange(len(cases), dtype=torch.int32, device=dev),
+                          positions=q_pos.to(dev), start_pos=q_pos.to(dev), extras={}, max_context_len=n,
+                          cu_tokens=torch.arange(len(cases) + 1, dtype=torch.int32, device=dev),
+                          seqs=[SeqSlice(None, 0, p, 1, i) for i, (p, _k) in enumerate(cases)], num_seqs=len(cases))
+    table = order.to(torch.int32).view(1, -1).repeat(len(cases), 1).contiguous().to(dev)
     qd = q.to(dev)
     out = ops.latent_attention(ctx, qd[:, :, :rank], qd[:, :, rank:], pages.to(dev), table, rank, rot, page, 1.0)
     out = out.float().cpu()
@@ -330,6 +334,71 @@ def test_latent_attention_kernel_far_key_page_borders_and_first_tokens(dtype):
         assert (out[i].double() - want).abs().max() < tol, f"query at {pos}, key {key}"
         if pos != key or pos == 0:
             assert (out[i, -1].double() - rows[key, :rank].double()).abs().max() < 0.05
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,rank,rot", [(6, 96, 32), (40, 64, 16), (16, 256, 64), (3, 32, 0)])
+def test_latent_attention_tensor_core_kernel_against_plain_softmax(heads, rank, rot):
+    """bfloat16 sizes the tensor-core kernel takes: a decode batch of requests of unequal
+    lengths (1, 2, 31, 32, 33, 300, 1000 keys; the key range cut into several blocks) and a
+    portion of 77 tokens behind 200 cached ones, pages scattered, unwritten rows poisoned."""
+    from types import SimpleNamespace
+    from helios_b200.csrc import ops
+    from helios_b200.engine.batch import SeqSlice
+
+    dev, page = "cuda", 16
+    g = torch.Generator().manual_seed(heads)
+    lens = [1, 2, 31, 32, 33, 300, 1000]
+    n_pages = sum(-(-n // page) for n in lens) + 20
+    pages = torch.full((n_pages + 2, 1, page, rank + rot), float("nan"), dtype=torch.bfloat16)
+    order = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-n // page) for n in lens)
+    rows_of, table = [], torch.full((len(lens) + 1, width), -1, dtype=torch.int32)
+    for i, n in enumerate(lens + [277]):
+        rows = (torch.randn(n, rank + rot, generator=g) * 0.5).to(torch.bfloat16)
+        rows_of.append(rows)
+        if i == len(lens):
+            table = torch.cat([table[:len(lens)], torch.full((1, width), -1, dtype=torch.int32)])
+        for j in range(-(-n // page)):
+            pg = order.pop()
+            table[i, j] = pg
+            chunk = rows[j * page:(j + 1) * page]
+            pages[pg, 0, :len(chunk)] = chunk
+    pages, table_d = pages.to(dev), table.contiguous().to(dev)
+
+    def run(seq_ids, starts, counts, max_ctx):
+        T = sum(counts)
+        q = (torch.randn(T, heads, rank + rot, generator=g) * 0.7).to(torch.bfloat16)
+        seq_of_token = torch.tensor([i for i, c in enumerate(counts) for _ in range(c)], dtype=torch.int32)
+        positions = torch.tensor([s + k for s, c in zip(starts, counts) for k in range(c)], dtype=torch.int32)
+        cu = torch.tensor([sum(counts[:i]) for i in range(len(counts) + 1)], dtype=torch.int32)
+        ctx = SimpleNamespace(seq_of_token=seq_of_token.to(dev), positions=positions.to(dev), cu_tokens=cu.to(dev),
+                              start_pos=torch.tensor(starts, dtype=torch.int32, device=dev), extras={},
+                              seqs=[SeqSlice(None, 0, s, c, int(cu[i])) for i, (s, c) in enumerate(zip(starts, counts))],
+                              max_context_len=max_ctx, num_seqs=len(counts))
+        qd = q.to(dev)
+        tab = table_d[seq_ids].contiguous()
+        got = ops.latent_attention(ctx, qd[:, :, :rank], qd[:, :, rank:], pages, tab, rank, rot, page, 0.3)
+        ops.LATENT_ATTENTION_TENSOR_CORES = False
+        try:
+            plain_kernel = ops.latent_attention(ctx, qd[:, :, :rank], qd[:, :, rank:], pages, tab, rank, rot, page, 0.3)
+        finally:
+            ops.LATENT_ATTENTION_TENSOR_CORES = True
+        got, plain_kernel = got.float().cpu().double(), plain_kernel.float().cpu().double()
+        assert torch.isfinite(got).all()
+        t = 0
+        for i, (sid, s0, c) in enumerate(zip(seq_ids, starts, counts)):
+            rows = rows_of[sid].double()
+            for k in range(c):
+                sc = torch.einsum("hd,jd->hj", q[t].double(), rows[:s0 + k + 1]) * 0.3
+                want = torch.softmax(sc, -1) @ rows[:s0 + k + 1, :rank]
+                assert (got[t] - want).abs().max() < 2e-2, f"request {sid}, position {s0 + k}"
+                assert (plain_kernel[t] - want).abs().max() < 2e-2
+                t += 1
+
+    run(list(range(len(lens))), [n - 1 for n in lens], [1] * len(lens), 1000)      # decode, ranges split
+    run([len(lens)], [200], [77], 277)                                             # a portion behind a cached prefix
+    run([5, 2, 6], [290, 0, 990], [10, 31, 10], 1000)                              # mixed
 
 
 @pytest.mark.gpu
