@@ -13,8 +13,8 @@
 //
 // Kernels: `causal_conv_silu` (short causal convolution over time per channel + silu, the
 // taps - 1 inputs before a step's first token taken from the request's slot),
-// `causal_conv_state` (leaves the last taps - 1 inputs in the slot), `delta_rule` (the
-// recurrence) and `gated_rmsnorm` (o / rms(o) * weight * sigmoid(gate) per head).
+// `causal_conv_state` (leaves the last taps - 1 inputs in the slot), `delta_prepare` and
+// `delta_rule` (the recurrence) and `gated_rmsnorm` (o / rms(o) * weight * sigmoid(gate) per head).
 #include "common.cuh"
 
 // ---------------------------------------------------------------- short convolution
@@ -96,123 +96,221 @@ HB_EXPORT int hb_causal_conv_silu(void* out, const void* x, int ld, const float*
 }
 
 // ---------------------------------------------------------------- the recurrence
+// Two kernels.  `delta_prepare` is parallel over (token, head): unit-norm k and q (q also
+// times dk^-1/2), the decays g = exp(-exp(A_log) softplus(a + dt_bias)) and the write strength
+// beta = sigmoid(b), all float32, left as kqg [T, heads, 3, dkp] (dkp = dk rounded up to 4;
+// the padding holds k = q = 0, g = 1) and beta [T, heads].  `delta_rule` then walks each
+// request's tokens in order: a block owns 64 columns of one head's S, a quad of threads one
+// column in registers (a quarter of its dk rows each); the staged rows of 16 tokens arrive in
+// shared memory by 16-byte cp.async one chunk ahead, the values of the next chunk wait in
+// registers, and the two sums over dk run as four partial sums a thread and two shuffles
+// (their order depends on dk alone, not on the step or the batch).
 constexpr int DR_CHUNK = 16;        // tokens staged in shared memory at a time
 constexpr int DR_COLS = 64;         // columns of S (threads) a block owns
 
-// qkv [T, qkv_ld]: q at q_off + kh * dk, k at k_off + kh * dk, v at v_off + h * dv
-// (after convolution and silu).  beta_raw [T, beta_ld] at column h (before the sigmoid),
-// a_raw [T, a_ld] at column h * dk (before dt_bias and softplus).  S of a slot at
-// state + slot * state_stride, [heads, dk, dv].  o [T, heads * dv] float32.
-template <typename T, int DK>
-__global__ void __launch_bounds__(DR_COLS)
-delta_rule_kernel(float* __restrict__ o, const T* __restrict__ qkv, int qkv_ld, int q_off, int k_off,
-                  int v_off, const T* __restrict__ beta_raw, int beta_ld,
-                  const T* __restrict__ a_raw, int a_ld, const float* __restrict__ a_log,
-                  const float* __restrict__ dt_bias, float* __restrict__ state, long state_stride,
-                  const int* __restrict__ cu_tokens, const int* __restrict__ slots, int heads,
-                  int kv_heads, int dk, int dv) {
+__device__ __forceinline__ void dr_cp_async16(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+
+// qkv [T, qkv_ld]: q at q_off + kh * dk, k at k_off + kh * dk (after convolution and silu).
+// beta_raw [T, beta_ld] at column h (before the sigmoid), a_raw [T, a_ld] at column h * dk
+// (before dt_bias and softplus).
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(float* __restrict__ kqg, float* __restrict__ beta, const T* __restrict__ qkv,
+                     int qkv_ld, int q_off, int k_off, const T* __restrict__ beta_raw, int beta_ld,
+                     const T* __restrict__ a_raw, int a_ld, const float* __restrict__ a_log,
+                     const float* __restrict__ dt_bias, int n_rows, int heads, int kv_heads, int dk,
+                     int dkp) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float sm[];
-  float* ks = sm;                              // [CHUNK][dk]
-  float* qs = ks + DR_CHUNK * dk;              // [CHUNK][dk]
-  float* gs = qs + DR_CHUNK * dk;              // [CHUNK][dk]
-  float* vs = gs + DR_CHUNK * dk;              // [CHUNK][DR_COLS]
-  float* bs = vs + DR_CHUNK * DR_COLS;         // [CHUNK]
-  const int s = blockIdx.x, h = blockIdx.y;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  const int t = row / heads, h = row - t * heads;
   const int kh = h / (heads / kv_heads);
-  const int col = blockIdx.z * DR_COLS + threadIdx.x;
+  const T* kr = qkv + (size_t)t * qkv_ld + k_off + (size_t)kh * dk;
+  const T* qr = qkv + (size_t)t * qkv_ld + q_off + (size_t)kh * dk;
+  float kk = 0.f, qq = 0.f;
+  for (int i = lane; i < dk; i += 32) {
+    const float kv = to_float(kr[i]), qv = to_float(qr[i]);
+    kk += kv * kv;
+    qq += qv * qv;
+  }
+  const float kn = rsqrtf(warp_sum(kk) + 1e-6f);
+  const float qn = rsqrtf(warp_sum(qq) + 1e-6f) * rsqrtf((float)dk);
+  const float rate = expf(a_log[h]);
+  float* dst = kqg + (size_t)row * 3 * dkp;
+  for (int i = lane; i < dkp; i += 32) {
+    float kv = 0.f, qv = 0.f, gv = 1.f;
+    if (i < dk) {
+      kv = to_float(kr[i]) * kn;
+      qv = to_float(qr[i]) * qn;
+      const float a = to_float(a_raw[(size_t)t * a_ld + (size_t)h * dk + i]) + dt_bias[(size_t)h * dk + i];
+      const float sp = a > 20.f ? a : log1pf(expf(a));
+      gv = expf(-rate * sp);
+    }
+    dst[i] = kv;
+    dst[dkp + i] = qv;
+    dst[2 * dkp + i] = gv;
+  }
+  if (lane == 0) beta[row] = 1.f / (1.f + expf(-to_float(beta_raw[(size_t)t * beta_ld + h])));
+}
+
+// v at qkv[t, v_off + h * dv + col].  S of a slot at state + slot * state_stride,
+// [heads, dk, dv].  o [T, heads * dv] float32.  A column of S is held by the four threads of
+// a quad: thread `part` keeps the rows 16 m + 4 part .. + 3 (the float4 groups m * 4 + part),
+// and the two sums over dk are finished with two shuffles.
+template <typename T, int DK>
+__global__ void __launch_bounds__(DR_COLS * 4)
+delta_rule_kernel(float* __restrict__ o, const float* __restrict__ kqg, const float* __restrict__ beta,
+                  const T* __restrict__ qkv, int qkv_ld, int v_off, float* __restrict__ state,
+                  long state_stride, const int* __restrict__ cu_tokens, const int* __restrict__ slots,
+                  int heads, int dk, int dkp, int dv) {
+  // No early release of the next kernel here: this kernel runs long on few blocks, and the
+  // blocks of a dependent that is launched at its start would sit on the SMs, waiting, beside
+  // it for all that time (2,048 tokens of one request: 2.54 ms with the early release, 1.10 without).
+  pdl_wait();
+  extern __shared__ __align__(16) float dr_sm[];
+  constexpr int THREADS = DR_COLS * 4, G = DK / 16;   // float4 groups a thread holds
+  const int row_f = 3 * dkp;                        // staged floats a token
+  float* stage_buf = dr_sm;                         // [2][CHUNK][3 dkp]
+  float* bs = dr_sm + 2 * DR_CHUNK * row_f;         // [2][CHUNK]
+  float* vs = bs + 2 * DR_CHUNK;                    // [2][CHUNK][COLS]
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int part = threadIdx.x & 3, lcol = threadIdx.x >> 2;
+  const int col = blockIdx.z * DR_COLS + lcol;
   const bool live = col < dv;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = cu_tokens[s], n = cu_tokens[s + 1] - t0;
   float* S_g = state + (size_t)slots[s] * state_stride + (size_t)h * dk * dv;
-  const float decay_rate = expf(a_log[h]);
-  const float q_scale = rsqrtf((float)dk);
+  const T* v_col = qkv + v_off + (size_t)h * dv + (live ? col : 0);
 
-  float S[DK];
+  float S[G][4];
 #pragma unroll
-  for (int i = 0; i < DK; ++i) S[i] = (live && i < dk) ? S_g[(size_t)i * dv + col] : 0.f;
+  for (int m = 0; m < G; ++m)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = 16 * m + 4 * part + e;
+      S[m][e] = (live && i < dk) ? S_g[(size_t)i * dv + col] : 0.f;
+    }
 
+  auto stage = [&](int c0, int b) {
+    const int nc = min(DR_CHUNK, n - c0);
+    const int vecs = row_f / 4;
+    float* dst = stage_buf + (size_t)b * DR_CHUNK * row_f;
+    for (int idx = threadIdx.x; idx < nc * vecs; idx += THREADS) {
+      const int j = idx / vecs, v = idx - j * vecs;
+      dr_cp_async16(dst + j * row_f + v * 4, kqg + ((size_t)(t0 + c0 + j) * heads + h) * row_f + v * 4);
+    }
+    for (int j = threadIdx.x; j < nc; j += THREADS) bs[b * DR_CHUNK + j] = beta[(size_t)(t0 + c0 + j) * heads + h];
+  };
+  // the quad's thread `part` fetches the values of tokens part, part + 4, ... of a chunk
+  float v_next[DR_CHUNK / 4];
+  auto fetch_v = [&](int c0) {
+#pragma unroll
+    for (int jj = 0; jj < DR_CHUNK / 4; ++jj) {
+      const int j = 4 * jj + part;
+      v_next[jj] = (c0 + j < n) ? to_float(v_col[(size_t)(t0 + c0 + j) * qkv_ld]) : 0.f;
+    }
+  };
+
+  if (n > 0) {
+    stage(0, 0);
+    fetch_v(0);
+  }
+  asm volatile("cp.async.commit_group;\n" ::);
+  int b = 0;
   for (int c0 = 0; c0 < n; c0 += DR_CHUNK) {
     const int nc = min(DR_CHUNK, n - c0);
+    asm volatile("cp.async.wait_group 0;\n" ::);
+#pragma unroll
+    for (int jj = 0; jj < DR_CHUNK / 4; ++jj) vs[(b * DR_CHUNK + 4 * jj + part) * DR_COLS + lcol] = v_next[jj];
     __syncthreads();
-    // stage the chunk: unit-norm k and q, decays, values, write strengths
-    for (int j = warp; j < nc; j += DR_COLS / 32) {
-      const size_t t = (size_t)(t0 + c0 + j);
-      const T* kr = qkv + t * qkv_ld + k_off + (size_t)kh * dk;
-      const T* qr = qkv + t * qkv_ld + q_off + (size_t)kh * dk;
-      float kk = 0.f, qq = 0.f;
-      for (int i = lane; i < dk; i += 32) {
-        const float kv = to_float(kr[i]), qv = to_float(qr[i]);
-        kk += kv * kv;
-        qq += qv * qv;
-      }
-      const float kn = rsqrtf(warp_sum(kk) + 1e-6f), qn = rsqrtf(warp_sum(qq) + 1e-6f) * q_scale;
-      for (int i = lane; i < dk; i += 32) {
-        ks[j * dk + i] = to_float(kr[i]) * kn;
-        qs[j * dk + i] = to_float(qr[i]) * qn;
-        const float a = to_float(a_raw[t * a_ld + (size_t)h * dk + i]) + dt_bias[(size_t)h * dk + i];
-        const float sp = a > 20.f ? a : log1pf(expf(a));
-        gs[j * dk + i] = expf(-decay_rate * sp);
-      }
-      if (lane == 0) bs[j] = 1.f / (1.f + expf(-to_float(beta_raw[t * beta_ld + h])));
+    if (c0 + DR_CHUNK < n) {
+      stage(c0 + DR_CHUNK, b ^ 1);
+      fetch_v(c0 + DR_CHUNK);
     }
-    for (int idx = threadIdx.x; idx < nc * DR_COLS; idx += DR_COLS) {
-      const int j = idx / DR_COLS, cc = idx - j * DR_COLS;
-      const int vc = blockIdx.z * DR_COLS + cc;
-      vs[idx] = vc < dv ? to_float(qkv[(size_t)(t0 + c0 + j) * qkv_ld + v_off + (size_t)h * dv + vc]) : 0.f;
-    }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;\n" ::);
+    const float* rows = stage_buf + (size_t)b * DR_CHUNK * row_f;
+#pragma unroll 2
     for (int j = 0; j < nc; ++j) {
-      const float* kj = ks + j * dk;
-      const float* qj = qs + j * dk;
-      const float* gj = gs + j * dk;
-      float dot = 0.f;
+      const float4* k4 = reinterpret_cast<const float4*>(rows + j * row_f) + part;
+      const float4* q4 = reinterpret_cast<const float4*>(rows + j * row_f + dkp) + part;
+      const float4* g4 = reinterpret_cast<const float4*>(rows + j * row_f + 2 * dkp) + part;
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < DK; ++i)
-        if (i < dk) {
-          S[i] *= gj[i];
-          dot = fmaf(S[i], kj[i], dot);
+      for (int m = 0; m < G; ++m)
+        if (16 * m + 4 * part < dkp) {
+          const float4 g = g4[4 * m], k = k4[4 * m];
+          S[m][0] *= g.x; d0 = fmaf(S[m][0], k.x, d0);
+          S[m][1] *= g.y; d1 = fmaf(S[m][1], k.y, d1);
+          S[m][2] *= g.z; d2 = fmaf(S[m][2], k.z, d2);
+          S[m][3] *= g.w; d3 = fmaf(S[m][3], k.w, d3);
         }
-      const float u = bs[j] * (vs[j * DR_COLS + threadIdx.x] - dot);
-      float out = 0.f;
+      float dot = (d0 + d1) + (d2 + d3);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      const float u = bs[b * DR_CHUNK + j] * (vs[(b * DR_CHUNK + j) * DR_COLS + lcol] - dot);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < DK; ++i)
-        if (i < dk) {
-          S[i] = fmaf(kj[i], u, S[i]);
-          out = fmaf(S[i], qj[i], out);
+      for (int m = 0; m < G; ++m)
+        if (16 * m + 4 * part < dkp) {
+          const float4 k = k4[4 * m], q = q4[4 * m];
+          S[m][0] = fmaf(k.x, u, S[m][0]); o0 = fmaf(S[m][0], q.x, o0);
+          S[m][1] = fmaf(k.y, u, S[m][1]); o1 = fmaf(S[m][1], q.y, o1);
+          S[m][2] = fmaf(k.z, u, S[m][2]); o2 = fmaf(S[m][2], q.z, o2);
+          S[m][3] = fmaf(k.w, u, S[m][3]); o3 = fmaf(S[m][3], q.w, o3);
         }
-      if (live) o[(size_t)(t0 + c0 + j) * heads * dv + (size_t)h * dv + col] = out;
+      float out = (o0 + o1) + (o2 + o3);
+      out += __shfl_xor_sync(0xffffffffu, out, 1);
+      out += __shfl_xor_sync(0xffffffffu, out, 2);
+      if (live && part == 0) o[(size_t)(t0 + c0 + j) * heads * dv + (size_t)h * dv + col] = out;
     }
+    b ^= 1;
   }
+  asm volatile("cp.async.wait_group 0;\n" ::);
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i)
-      if (i < dk) S_g[(size_t)i * dv + col] = S[i];
+    for (int m = 0; m < G; ++m)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = 16 * m + 4 * part + e;
+        if (i < dk) S_g[(size_t)i * dv + col] = S[m][e];
+      }
   }
 }
 
-HB_EXPORT int hb_delta_rule(float* o, const void* qkv, int qkv_ld, int q_off, int k_off, int v_off,
-                            const void* beta_raw, int beta_ld, const void* a_raw, int a_ld,
+// scratch: n_tokens * heads * (3 * dkp + 1) floats, dkp = dk rounded up to a multiple of 4
+HB_EXPORT int hb_delta_rule(float* o, float* scratch, const void* qkv, int qkv_ld, int q_off, int k_off,
+                            int v_off, const void* beta_raw, int beta_ld, const void* a_raw, int a_ld,
                             const float* a_log, const float* dt_bias, float* state,
-                            long state_stride, const int* cu_tokens, const int* slots, int n_seqs,
-                            int heads, int kv_heads, int dk, int dv, int act_dt,
+                            long state_stride, const int* cu_tokens, const int* slots, int n_tokens,
+                            int n_seqs, int heads, int kv_heads, int dk, int dv, int act_dt,
                             cudaStream_t stream) {
-  if (n_seqs <= 0) return HB_OK;
+  if (n_seqs <= 0 || n_tokens <= 0) return HB_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dk <= 0 || dk > 256 || dv <= 0 ||
-      heads > 65535)
+      heads > 65535 || scratch == nullptr)
     return HB_BAD_ARGUMENT;
+  const int dkp = (dk + 3) / 4 * 4;
+  float* kqg = scratch;
+  float* beta = scratch + (size_t)n_tokens * heads * 3 * dkp;
+  const int n_rows = n_tokens * heads;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(delta_prepare_kernel<TA>, dim3((n_rows + 3) / 4), dim3(128), 0, stream, kqg, beta,
+              (const TA*)qkv, qkv_ld, q_off, k_off, (const TA*)beta_raw, beta_ld, (const TA*)a_raw, a_ld,
+              a_log, dt_bias, n_rows, heads, kv_heads, dk, dkp));
   dim3 grid(n_seqs, heads, (dv + DR_COLS - 1) / DR_COLS);
-  const size_t smem = ((size_t)DR_CHUNK * (3 * dk + DR_COLS) + DR_CHUNK) * sizeof(float);
+  const size_t smem = ((size_t)2 * DR_CHUNK * 3 * dkp + 2 * DR_CHUNK + 2 * DR_CHUNK * DR_COLS) * sizeof(float);
 #define HB_DR_LAUNCH(DKMAX)                                                                       \
   HB_DISPATCH_DTYPE(act_dt, TA,                                                                   \
     if (smem > 48 * 1024)                                                                         \
       cudaFuncSetAttribute(delta_rule_kernel<TA, DKMAX>,                                          \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
-    hb_launch(delta_rule_kernel<TA, DKMAX>, grid, dim3(DR_COLS), smem, stream, o, (const TA*)qkv, \
-              qkv_ld, q_off, k_off, v_off, (const TA*)beta_raw, beta_ld, (const TA*)a_raw, a_ld,  \
-              a_log, dt_bias, state, state_stride, cu_tokens, slots, heads, kv_heads, dk, dv))
-  if (dk <= 32) HB_DR_LAUNCH(32);
+    hb_launch(delta_rule_kernel<TA, DKMAX>, grid, dim3(DR_COLS * 4), smem, stream, o,             \
+              (const float*)kqg, (const float*)beta, (const TA*)qkv, qkv_ld, v_off, state,        \
+              state_stride, cu_tokens, slots, heads, dk, dkp, dv))
+  if (dk <= 16) HB_DR_LAUNCH(16);
+  else if (dk <= 32) HB_DR_LAUNCH(32);
   else if (dk <= 64) HB_DR_LAUNCH(64);
   else if (dk <= 128) HB_DR_LAUNCH(128);
   else HB_DR_LAUNCH(256);

@@ -1180,6 +1180,19 @@ def head_gemm(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 LATENT_ATTENTION_TENSOR_CORES = True
 
 
+def linear_rows(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``linear`` for rows that are a column slice of wider rows (last dimension contiguous):
+    no copy is made.  Few tokens and float32 run on ``head_gemm`` with one head, more tokens
+    in bfloat16 on the library, which takes the row stride."""
+    if x.is_contiguous():
+        return linear(x, weight)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("linear_rows: rows must be contiguous in their last dimension")
+    if x.dtype == torch.bfloat16 and x.shape[0] >= HEAD_GEMM_LIBRARY_TOKENS:
+        return torch.nn.functional.linear(x, weight)
+    return head_gemm(x.unsqueeze(1), weight.unsqueeze(0)).view(x.shape[0], weight.shape[0])
+
+
 def latent_attention(ctx, q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tensor,
                      block_table: torch.Tensor, rank: int, rot: int, page_size: int,
                      scale: float) -> torch.Tensor:
@@ -1283,12 +1296,14 @@ def delta_rule(ctx, qkv: torch.Tensor, offsets, beta_raw: torch.Tensor, a_raw: t
         raise KernelError("delta_rule: sizes do not fit (key size at most 256)")
     T = qkv.shape[0]
     o = torch.empty((T, heads * dv), dtype=torch.float32, device=qkv.device)
+    # unit-norm k and q, decays and write strengths of every (token, head), float32
+    scratch = torch.empty((T * heads * (3 * (-(-dk // 4) * 4) + 1),), dtype=torch.float32, device=qkv.device)
     f = _fn("delta_rule", "hb_delta_rule",
-            [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
-             c_void_p, c_void_p, _LONG, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(o), _p(qkv), qkv.shape[1], offsets[0], offsets[1], offsets[2], _p(beta_raw),
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+             c_void_p, c_void_p, _LONG, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(o), _p(scratch), _p(qkv), qkv.shape[1], offsets[0], offsets[1], offsets[2], _p(beta_raw),
            beta_raw.stride(0), _p(a_raw), a_raw.stride(0), _p(a_log), _p(dt_bias), _p(state),
-           state.stride(0), _p(ctx.cu_tokens), _p(ctx.slots), ctx.num_seqs, heads, kv_heads, dk, dv,
+           state.stride(0), _p(ctx.cu_tokens), _p(ctx.slots), T, ctx.num_seqs, heads, kv_heads, dk, dv,
            _dt(qkv.dtype), _stream()), "delta_rule")
     return o
 

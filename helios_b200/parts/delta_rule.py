@@ -74,8 +74,8 @@ class GatedDeltaMixer(Mixer):
         C, Ra, Rg = self.conv_channels, self.decay_rank, self.gate_rank
         proj = ops.linear(x, self.w_in)
         qkv = ops.causal_conv_silu(ctx, proj, C, self.conv_w, state[:, self.state_floats:])
-        a_raw = ops.linear(proj[:, C:C + Ra].contiguous(), self.w_a2)
-        gate = ops.linear(proj[:, C + Ra:C + Ra + Rg].contiguous(), self.w_g2)
+        a_raw = ops.linear_rows(proj[:, C:C + Ra], self.w_a2)
+        gate = ops.linear_rows(proj[:, C + Ra:C + Ra + Rg], self.w_g2)
         qk = self.kv_heads * self.dk
         o = ops.delta_rule(ctx, qkv, (0, qk, 2 * qk), proj[:, C + Ra + Rg:], a_raw, self.a_log,
                            self.dt_bias, state[:, :self.state_floats], self.heads, self.kv_heads,
