@@ -167,9 +167,11 @@ delta_rule_kernel(float* __restrict__ o, const float* __restrict__ kqg, const fl
                   const T* __restrict__ qkv, int qkv_ld, int v_off, float* __restrict__ state,
                   long state_stride, const int* __restrict__ cu_tokens, const int* __restrict__ slots,
                   int heads, int dk, int dkp, int dv) {
-  // No early release of the next kernel here: this kernel runs long on few blocks, and the
-  // blocks of a dependent that is launched at its start would sit on the SMs, waiting, beside
-  // it for all that time (2,048 tokens of one request: 2.54 ms with the early release, 1.10 without).
+  // Neither launched early nor releasing the next kernel early: a long prompt of one request
+  // is a few blocks that run for a millisecond.  Launched while the kernel before still holds
+  // the SMs they land two to an SM wherever room is, and share its issue slots for all that
+  // time (2,048 tokens of one request: 2.54 ms against 1.10 ms on idle SMs); the blocks of a
+  // dependent released at the start would wait beside them as long.
   pdl_wait();
   extern __shared__ __align__(16) float dr_sm[];
   constexpr int THREADS = DR_COLS * 4, G = DK / 16;   // float4 groups a thread holds
@@ -306,9 +308,9 @@ HB_EXPORT int hb_delta_rule(float* o, float* scratch, const void* qkv, int qkv_l
     if (smem > 48 * 1024)                                                                         \
       cudaFuncSetAttribute(delta_rule_kernel<TA, DKMAX>,                                          \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
-    hb_launch(delta_rule_kernel<TA, DKMAX>, grid, dim3(DR_COLS * 4), smem, stream, o,             \
-              (const float*)kqg, (const float*)beta, (const TA*)qkv, qkv_ld, v_off, state,        \
-              state_stride, cu_tokens, slots, heads, dk, dkp, dv))
+    delta_rule_kernel<TA, DKMAX><<<grid, dim3(DR_COLS * 4), smem, stream>>>(                      \
+        o, (const float*)kqg, (const float*)beta, (const TA*)qkv, qkv_ld, v_off, state,           \
+        state_stride, cu_tokens, slots, heads, dk, dkp, dv))
   if (dk <= 16) HB_DR_LAUNCH(16);
   else if (dk <= 32) HB_DR_LAUNCH(32);
   else if (dk <= 64) HB_DR_LAUNCH(64);

@@ -320,6 +320,9 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
     row_out[tid] = ok ? (tok0 + t_first + lt) * heads + h : -1;
   }
   __syncthreads();
+  // rows are handed out from 0 on: a group whose first row is none has none (steps of single
+  // tokens with 16 heads or fewer fill one group only)
+  const bool group_live = row_out[rg * 16] >= 0;
   for (int idx = tid; idx < LM_ROWS * D; idx += 256) {
     const int r = idx / D, d = idx - r * D;
     __nv_bfloat16 v = __float2bfloat16_rn(0.f);
@@ -363,8 +366,8 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
     if (kt + 1 < kt_hi) load_tile(kt + 1, buf ^ 1);
     cp_async_commit();
     const __nv_bfloat16* kt_s = k_s + (size_t)buf * LM_KEYS * RS;
-    // scores of 16 rows against 8 keys
-    {
+    // scores of 16 rows against 8 keys (a row group without rows only keeps the barriers)
+    if (group_live) {
       float c[4] = {0.f, 0.f, 0.f, 0.f};
       const __nv_bfloat16* krow = kt_s + (8 * cq + g) * RS + 2 * t4;
       const __nv_bfloat16* qbase = q_s + (rg * 16 + (lane & 15)) * RS + (lane >> 4) * 8;
@@ -384,6 +387,10 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
       s_s[rb * LM_SPAD + 8 * cq + 2 * t4 + 1] = key + 1 <= pb ? c[3] * scale_log2 : -INFINITY;
     }
     __syncthreads();
+    if (!group_live) {
+      buf ^= 1;
+      continue;
+    }
     // online softmax over the row group's 16 x 32 scores, then P V for this warp's columns
     uint32_t pfrag[2][4];
     {
