@@ -320,7 +320,7 @@ def design_configs(size):
         width, heads, hd, rank, ff, experts, top, eff, vocab = 2048, 16, 128, 512, 8192, 32, 4, 2048, 32000
     else:
         width, heads, hd, rank, ff, experts, top, eff, vocab = 1024, 8, 64, 256, 4096, 16, 2, 2048, 32000
-    rot = {"base": 500000.0, "dims": hd // 2, "scaling": {"factor": 8.0, "fast": 32.0, "slow": 1.0, "original": 4096}}
+    rot = {"base": 10000.0, "dims": hd // 2, "scaling": {"factor": 4.0, "fast": 32.0, "slow": 1.0, "original": 4096}}
     latent = {"type": "latent_attention",
               "mixer": {"heads": heads, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": rank,
                         "scale": (hd + hd // 2) ** -0.5, "rot": rot}}

@@ -256,7 +256,7 @@ def test_yarn_frequencies_and_factor():
     from helios_b200.parts.rotary import yarn_attention_factor, yarn_frequencies
 
     for rot in ({"base": 10000.0, "dims": 8, "scaling": YARN},
-                {"base": 500000.0, "dims": 32, "scaling": {"factor": 8.0, "fast": 32.0, "slow": 1.0, "original": 2048}},
+                {"base": 250000.0, "dims": 48, "scaling": {"factor": 6.0, "fast": 24.0, "slow": 2.0, "original": 1024}},
                 {"base": 1000.0, "dims": 24, "scaling": {"factor": 16.0, "fast": 8.0, "slow": 1.0, "original": 32}}):
         s = rot["scaling"]
         want, factor = pz.rotary_frequencies(rot)
@@ -266,9 +266,9 @@ def test_yarn_frequencies_and_factor():
         plain = rot["base"] ** (-2.0 * torch.arange(rot["dims"] // 2, dtype=torch.float64) / rot["dims"])
         assert torch.all(got <= plain * (1 + 1e-12)) and torch.all(got >= plain / s["factor"] * (1 - 1e-12))
     # some pair keeps its frequency and some pair is fully stretched in the first case
-    got = yarn_frequencies(32, 500000.0, 8.0, 2048, 32.0, 1.0)
-    plain = 500000.0 ** (-2.0 * torch.arange(16, dtype=torch.float64) / 32)
-    assert got[0] == plain[0] and got[-1] == pytest.approx(float(plain[-1]) / 8.0)
+    got = yarn_frequencies(64, 10000.0, 4.0, 512, 32.0, 1.0)
+    plain = 10000.0 ** (-2.0 * torch.arange(32, dtype=torch.float64) / 64)
+    assert got[0] == plain[0] and got[-1] == pytest.approx(float(plain[-1]) / 4.0)
 
 
 def test_toy_model_of_the_design_from_the_command_line(tmp_path):
@@ -337,7 +337,7 @@ def test_latent_attention_kernel_far_key_page_borders_and_first_tokens(dtype):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("heads,rank,rot", [(6, 96, 32), (40, 64, 16), (16, 256, 64), (3, 32, 0)])
+@pytest.mark.parametrize("heads,rank,rot", [(5, 160, 48), (40, 64, 16), (16, 256, 64), (3, 32, 0)])
 def test_latent_attention_tensor_core_kernel_against_plain_softmax(heads, rank, rot):
     """bfloat16 sizes the tensor-core kernel takes: a decode batch of requests of unequal
     lengths (1, 2, 31, 32, 33, 300, 1000 keys; the key range cut into several blocks) and a
