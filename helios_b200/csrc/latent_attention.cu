@@ -287,7 +287,7 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
                             const int* __restrict__ block_table, int bt_stride,
                             const int* __restrict__ q_tiles, const int* __restrict__ cu_tokens,
                             const int* __restrict__ start_pos, int heads, int heads_per_block,
-                            int tokens_per_tile, int rank, int rot, int page_size,
+                            int tokens_per_tile, int rank, int rot, int page_size, int page_shift,
                             float scale_log2, int n_splits) {
   pdl_launch_dependents();
   pdl_wait();
@@ -323,27 +323,40 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
   // rows are handed out from 0 on: a group whose first row is none has none (steps of single
   // tokens with 16 heads or fewer fill one group only)
   const bool group_live = row_out[rg * 16] >= 0;
-  for (int idx = tid; idx < LM_ROWS * D; idx += 256) {
-    const int r = idx / D, d = idx - r * D;
-    __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+  // a warp copies 4 query rows (index arithmetic once a row, not once a value)
+  for (int r = warp; r < LM_ROWS; r += 8) {
+    __nv_bfloat16* dst = q_s + r * RS;
     if (row_out[r] >= 0) {
       const int tg = row_out[r] / heads, h = row_out[r] - tg * heads;
-      v = d < rank ? q_lat[(size_t)tg * ql_t + (size_t)h * ql_h + d]
-                   : q_rot[(size_t)tg * qr_t + (size_t)h * qr_h + (d - rank)];
+      const __nv_bfloat16* ql = q_lat + (size_t)tg * ql_t + (size_t)h * ql_h;
+      const __nv_bfloat16* qr = q_rot + (size_t)tg * qr_t + (size_t)h * qr_h;
+      for (int d = lane; d < rank; d += 32) dst[d] = ql[d];
+      for (int d = lane; d < rot; d += 32) dst[rank + d] = qr[d];
+    } else {
+      for (int d = lane; d < D; d += 32) dst[d] = __float2bfloat16_rn(0.f);
     }
-    q_s[r * RS + d] = v;
   }
 
+  // Lane r finds the row of key kt * 32 + r (its page from the block table); warp w then
+  // copies rows 4 w .. 4 w + 3 in 16-byte pieces, the row's start handed over by shuffles:
+  // no division per piece.  Rows beyond the last key are zero-filled.
   const int vec_per_row = D / 8;
   auto load_tile = [&](int kt, int buf) {
     __nv_bfloat16* dst = k_s + (size_t)buf * LM_KEYS * RS;
-    for (int idx = tid; idx < LM_KEYS * vec_per_row; idx += 256) {
-      const int r = idx / vec_per_row, v = idx - r * vec_per_row;
-      const int key = kt * LM_KEYS + r;
-      const bool ok = key < n_keys;
-      const __nv_bfloat16* src = pages;
-      if (ok) src = pages + ((size_t)table[key / page_size] * page_size + key % page_size) * D + v * 8;
-      cp_async16(dst + r * RS + v * 8, src, ok ? 16 : 0);
+    const int key = kt * LM_KEYS + lane;
+    long long row_off = -1;
+    if (key < n_keys) {
+      const int pg = page_shift >= 0 ? key >> page_shift : key / page_size;
+      const int in_pg = page_shift >= 0 ? key & (page_size - 1) : key - pg * page_size;
+      row_off = ((long long)table[pg] * page_size + in_pg) * D;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 4 * warp + i;
+      const long long off = __shfl_sync(0xffffffffu, row_off, r);
+      const __nv_bfloat16* src = pages + (off < 0 ? 0 : off);
+      __nv_bfloat16* drow = dst + r * RS;
+      for (int v = lane; v < vec_per_row; v += 32) cp_async16(drow + v * 8, src + v * 8, off < 0 ? 0 : 16);
     }
   };
 
@@ -370,14 +383,29 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
     if (group_live) {
       float c[4] = {0.f, 0.f, 0.f, 0.f};
       const __nv_bfloat16* krow = kt_s + (8 * cq + g) * RS + 2 * t4;
+      // one ldmatrix.x4 gives the key fragments of two k-steps: matrix j = columns 8 j .. 8 j + 7
+      const __nv_bfloat16* kmat = kt_s + (8 * cq + (lane & 7)) * RS + (lane >> 3) * 8;
       const __nv_bfloat16* qbase = q_s + (rg * 16 + (lane & 15)) * RS + (lane >> 4) * 8;
-      for (int ks = 0; ks < ksteps; ++ks) {
+      // two accumulators: two chains of dependent mma instead of one
+      float c1[4] = {0.f, 0.f, 0.f, 0.f};
+      int ks = 0;
+      for (; ks + 1 < ksteps; ks += 2) {
+        uint32_t a0[4], a1[4], b[4];
+        ldmatrix_x4(a0, qbase + ks * 16);
+        ldmatrix_x4(a1, qbase + ks * 16 + 16);
+        ldmatrix_x4(b, kmat + ks * 16);
+        mma_bf16(c, a0, b[0], b[1]);
+        mma_bf16(c1, a1, b[2], b[3]);
+      }
+      if (ks < ksteps) {
         uint32_t a[4];
         ldmatrix_x4(a, qbase + ks * 16);
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
         const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
         mma_bf16(c, a, b0, b1);
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[e] += c1[e];
       const int key = kt * LM_KEYS + 8 * cq + 2 * t4;
       const int ra = rg * 16 + g, rb = ra + 8;
       const int pa = row_pos[ra], pb = row_pos[rb];
@@ -418,12 +446,14 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
           sum += p[r][j];
         }
         l[r] = l[r] * corr + sum;
+        if (corr != 1.f) {                 // the maximum moved: rare once a row has seen a few tiles
 #pragma unroll
-        for (int nt = 0; nt < LM_MAXNT; ++nt)
-          if (nt < ntq) {
-            acc[nt][2 * r] *= corr;
-            acc[nt][2 * r + 1] *= corr;
-          }
+          for (int nt = 0; nt < LM_MAXNT; ++nt)
+            if (nt < ntq) {
+              acc[nt][2 * r] *= corr;
+              acc[nt][2 * r + 1] *= corr;
+            }
+        }
       }
       // columns 2 t4 + 8 j of the 32 keys: j = 0, 1 belong to keys 0..15, j = 2, 3 to 16..31
 #pragma unroll
@@ -528,11 +558,14 @@ HB_EXPORT int hb_latent_attention_mma(void* out, float* part_acc, float* part_ml
     smem_set = smem;
   }
   const int head_groups = (heads + heads_per_block - 1) / heads_per_block;
+  int page_shift = -1;                               // log2 of a page size that is a power of two
+  for (int b = 0; b < 31; ++b)
+    if ((1 << b) == page_size) page_shift = b;
   hb_launch(latent_attention_mma_kernel, dim3(n_tiles, head_groups, n_splits), dim3(256), smem, stream,
             (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q_lat, ql_t, ql_h,
             (const __nv_bfloat16*)q_rot, qr_t, qr_h, (const __nv_bfloat16*)pages, block_table, bt_stride,
             q_tiles, cu_tokens, start_pos, heads, heads_per_block, tokens_per_tile, rank, rot, page_size,
-            scale * 1.4426950408889634f, n_splits);
+            page_shift, scale * 1.4426950408889634f, n_splits);
   if (n_splits > 1) {
     const int n_rows = n_tokens * heads;
     hb_launch(latent_attention_merge_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream,
