@@ -99,7 +99,7 @@ HB_EXPORT int hb_causal_conv_silu(void* out, const void* x, int ld, const float*
 // Two kernels.  `delta_prepare` is parallel over (token, head): unit-norm k and q (q also
 // times dk^-1/2), the decays g = exp(-exp(A_log) softplus(a + dt_bias)) and the write strength
 // beta = sigmoid(b), all float32, left as kqg [T, heads, 3, dkp] (dkp = dk rounded up to 4;
-// the padding holds k = q = 0, g = 1) and beta [T, heads].  `delta_rule` then walks each
+// the padding holds k = q = 0, g = 1) and (beta, k . q) [T, heads, 2].  `delta_rule` then walks each
 // request's tokens in order: a block owns 64 columns of one head's S, a quad of threads one
 // column in registers (a quarter of its dk rows each); the staged rows of 16 tokens arrive in
 // shared memory by 16-byte cp.async one chunk ahead, the values of the next chunk wait in
@@ -154,7 +154,14 @@ delta_prepare_kernel(float* __restrict__ kqg, float* __restrict__ beta, const T*
     dst[dkp + i] = qv;
     dst[2 * dkp + i] = gv;
   }
-  if (lane == 0) beta[row] = 1.f / (1.f + expf(-to_float(beta_raw[(size_t)t * beta_ld + h])));
+  // k . q of the unit vectors: the scan reads o = (g (.) S)^T q + u (k . q) off ONE pass over S
+  float kq = 0.f;
+  for (int i = lane; i < dk; i += 32) kq = fmaf(to_float(kr[i]), to_float(qr[i]), kq);
+  kq = warp_sum(kq) * kn * qn;
+  if (lane == 0) {
+    beta[2 * row] = 1.f / (1.f + expf(-to_float(beta_raw[(size_t)t * beta_ld + h])));
+    beta[2 * row + 1] = kq;
+  }
 }
 
 // v at qkv[t, v_off + h * dv + col].  S of a slot at state + slot * state_stride,
@@ -177,8 +184,8 @@ delta_rule_kernel(float* __restrict__ o, const float* __restrict__ kqg, const fl
   constexpr int THREADS = DR_COLS * 4, G = DK / 16;   // float4 groups a thread holds
   const int row_f = 3 * dkp;                        // staged floats a token
   float* stage_buf = dr_sm;                         // [2][CHUNK][3 dkp]
-  float* bs = dr_sm + 2 * DR_CHUNK * row_f;         // [2][CHUNK]
-  float* vs = bs + 2 * DR_CHUNK;                    // [2][CHUNK][COLS]
+  float* bs = dr_sm + 2 * DR_CHUNK * row_f;         // [2][CHUNK][2]: beta, k . q
+  float* vs = bs + 4 * DR_CHUNK;                    // [2][CHUNK][COLS]
   const int s = blockIdx.x, h = blockIdx.y;
   const int part = threadIdx.x & 3, lcol = threadIdx.x >> 2;
   const int col = blockIdx.z * DR_COLS + lcol;
@@ -204,7 +211,8 @@ delta_rule_kernel(float* __restrict__ o, const float* __restrict__ kqg, const fl
       const int j = idx / vecs, v = idx - j * vecs;
       dr_cp_async16(dst + j * row_f + v * 4, kqg + ((size_t)(t0 + c0 + j) * heads + h) * row_f + v * 4);
     }
-    for (int j = threadIdx.x; j < nc; j += THREADS) bs[b * DR_CHUNK + j] = beta[(size_t)(t0 + c0 + j) * heads + h];
+    for (int j = threadIdx.x; j < 2 * nc; j += THREADS)
+      bs[2 * b * DR_CHUNK + j] = beta[2 * ((size_t)(t0 + c0 + (j >> 1)) * heads + h) + (j & 1)];
   };
   // the quad's thread `part` fetches the values of tokens part, part + 4, ... of a chunk
   float v_next[DR_CHUNK / 4];
@@ -239,33 +247,36 @@ delta_rule_kernel(float* __restrict__ o, const float* __restrict__ kqg, const fl
       const float4* k4 = reinterpret_cast<const float4*>(rows + j * row_f) + part;
       const float4* q4 = reinterpret_cast<const float4*>(rows + j * row_f + dkp) + part;
       const float4* g4 = reinterpret_cast<const float4*>(rows + j * row_f + 2 * dkp) + part;
-      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      // one pass: S <- g (.) S with the sums S^T k and S^T q; then u, the read-out
+      // o = S^T q + u (k . q) (what S^T q is after the write), and the write S += k u, which
+      // nothing waits for until the next token's pass
+      float d0 = 0.f, d1 = 0.f, e0 = 0.f, e1 = 0.f;
+      float4 kk[G];
 #pragma unroll
       for (int m = 0; m < G; ++m)
         if (16 * m + 4 * part < dkp) {
-          const float4 g = g4[4 * m], k = k4[4 * m];
-          S[m][0] *= g.x; d0 = fmaf(S[m][0], k.x, d0);
-          S[m][1] *= g.y; d1 = fmaf(S[m][1], k.y, d1);
-          S[m][2] *= g.z; d2 = fmaf(S[m][2], k.z, d2);
-          S[m][3] *= g.w; d3 = fmaf(S[m][3], k.w, d3);
+          const float4 g = g4[4 * m], k = k4[4 * m], q = q4[4 * m];
+          kk[m] = k;
+          S[m][0] *= g.x; d0 = fmaf(S[m][0], k.x, d0); e0 = fmaf(S[m][0], q.x, e0);
+          S[m][1] *= g.y; d1 = fmaf(S[m][1], k.y, d1); e1 = fmaf(S[m][1], q.y, e1);
+          S[m][2] *= g.z; d0 = fmaf(S[m][2], k.z, d0); e0 = fmaf(S[m][2], q.z, e0);
+          S[m][3] *= g.w; d1 = fmaf(S[m][3], k.w, d1); e1 = fmaf(S[m][3], q.w, e1);
         }
-      float dot = (d0 + d1) + (d2 + d3);
+      float dot = d0 + d1, rd = e0 + e1;
       dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      rd += __shfl_xor_sync(0xffffffffu, rd, 1);
       dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-      const float u = bs[b * DR_CHUNK + j] * (vs[(b * DR_CHUNK + j) * DR_COLS + lcol] - dot);
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      rd += __shfl_xor_sync(0xffffffffu, rd, 2);
+      const float u = bs[2 * (b * DR_CHUNK + j)] * (vs[(b * DR_CHUNK + j) * DR_COLS + lcol] - dot);
+      const float out = fmaf(u, bs[2 * (b * DR_CHUNK + j) + 1], rd);
 #pragma unroll
       for (int m = 0; m < G; ++m)
         if (16 * m + 4 * part < dkp) {
-          const float4 k = k4[4 * m], q = q4[4 * m];
-          S[m][0] = fmaf(k.x, u, S[m][0]); o0 = fmaf(S[m][0], q.x, o0);
-          S[m][1] = fmaf(k.y, u, S[m][1]); o1 = fmaf(S[m][1], q.y, o1);
-          S[m][2] = fmaf(k.z, u, S[m][2]); o2 = fmaf(S[m][2], q.z, o2);
-          S[m][3] = fmaf(k.w, u, S[m][3]); o3 = fmaf(S[m][3], q.w, o3);
+          S[m][0] = fmaf(kk[m].x, u, S[m][0]);
+          S[m][1] = fmaf(kk[m].y, u, S[m][1]);
+          S[m][2] = fmaf(kk[m].z, u, S[m][2]);
+          S[m][3] = fmaf(kk[m].w, u, S[m][3]);
         }
-      float out = (o0 + o1) + (o2 + o3);
-      out += __shfl_xor_sync(0xffffffffu, out, 1);
-      out += __shfl_xor_sync(0xffffffffu, out, 2);
       if (live && part == 0) o[(size_t)(t0 + c0 + j) * heads * dv + (size_t)h * dv + col] = out;
     }
     b ^= 1;
@@ -282,7 +293,7 @@ delta_rule_kernel(float* __restrict__ o, const float* __restrict__ kqg, const fl
   }
 }
 
-// scratch: n_tokens * heads * (3 * dkp + 1) floats, dkp = dk rounded up to a multiple of 4
+// scratch: n_tokens * heads * (3 * dkp + 2) floats, dkp = dk rounded up to a multiple of 4
 HB_EXPORT int hb_delta_rule(float* o, float* scratch, const void* qkv, int qkv_ld, int q_off, int k_off,
                             int v_off, const void* beta_raw, int beta_ld, const void* a_raw, int a_ld,
                             const float* a_log, const float* dt_bias, float* state,
@@ -302,7 +313,7 @@ HB_EXPORT int hb_delta_rule(float* o, float* scratch, const void* qkv, int qkv_l
               (const TA*)qkv, qkv_ld, q_off, k_off, (const TA*)beta_raw, beta_ld, (const TA*)a_raw, a_ld,
               a_log, dt_bias, n_rows, heads, kv_heads, dk, dkp));
   dim3 grid(n_seqs, heads, (dv + DR_COLS - 1) / DR_COLS);
-  const size_t smem = ((size_t)2 * DR_CHUNK * 3 * dkp + 2 * DR_CHUNK + 2 * DR_CHUNK * DR_COLS) * sizeof(float);
+  const size_t smem = ((size_t)2 * DR_CHUNK * 3 * dkp + 4 * DR_CHUNK + 2 * DR_CHUNK * DR_COLS) * sizeof(float);
 #define HB_DR_LAUNCH(DKMAX)                                                                       \
   HB_DISPATCH_DTYPE(act_dt, TA,                                                                   \
     if (smem > 48 * 1024)                                                                         \

@@ -1297,7 +1297,7 @@ def delta_rule(ctx, qkv: torch.Tensor, offsets, beta_raw: torch.Tensor, a_raw: t
     T = qkv.shape[0]
     o = torch.empty((T, heads * dv), dtype=torch.float32, device=qkv.device)
     # unit-norm k and q, decays and write strengths of every (token, head), float32
-    scratch = torch.empty((T * heads * (3 * (-(-dk // 4) * 4) + 1),), dtype=torch.float32, device=qkv.device)
+    scratch = torch.empty((T * heads * (3 * (-(-dk // 4) * 4) + 2),), dtype=torch.float32, device=qkv.device)
     f = _fn("delta_rule", "hb_delta_rule",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
              c_void_p, c_void_p, _LONG, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
