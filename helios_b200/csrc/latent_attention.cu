@@ -266,9 +266,10 @@ HB_EXPORT int hb_latent_attention(void* out, const void* q_lat, long ql_t, long 
 //   8 warps = 2 row groups of 16 rows x 4 column quarters.  Scores: warp (rg, cq) computes
 //   the 16 x 8 block of its row group against keys 8 cq .. 8 cq + 7 (mma.sync m16n8k16 over
 //   rank + rot), masks by position and leaves it in shared memory.  After a barrier every
-//   warp of the row group reads the 16 x 32 scores, does the online-softmax step (float32,
-//   base 2) and adds P V for its quarter of the latent's columns: V is the first `rank`
-//   values of the very rows that were the keys, already in shared memory.
+//   warp of the row group does the online-softmax step (float32, base 2) for four of the 16
+//   rows and leaves P (bfloat16) and the rows' rescale factors in shared memory; after a
+//   second barrier every warp adds P V for its quarter of the latent's columns: V is the
+//   first `rank` values of the very rows that were the keys, already in shared memory.
 //
 // Key tiles arrive by 16-byte cp.async, one tile ahead.  The keys of a request are cut into
 // `n_splits` ranges (blockIdx.z), so that steps of few rows still fill the SMs; with more
@@ -276,8 +277,12 @@ HB_EXPORT int hb_latent_attention(void* out, const void* q_lat, long ql_t, long 
 // `latent_attention_merge` puts them together.
 #include "attention_mma.cuh"
 
-constexpr int LM_ROWS = 32, LM_KEYS = 32, LM_MAXNT = 16, LM_SPAD = 36;
+constexpr int LM_ROWS = 32, LM_KEYS = 32, LM_MAXNT = 16, LM_SPAD = 36, LM_PPAD = 40;
 
+// NTQ = rank / 32: the 8-column tiles of the latent a warp owns, a template parameter so that the
+// loops over them unroll without predicates (with a run-time count, integer arithmetic and
+// branches were most of the executed instructions and the tensor pipe a twentieth).
+template <int NTQ>
 __global__ void __launch_bounds__(256)
 latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_acc,
                             float* __restrict__ part_ml,
@@ -298,6 +303,10 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
   float* s_s = reinterpret_cast<float*>(k_s + 2 * LM_KEYS * RS);       // [32][LM_SPAD]
   int* row_pos = reinterpret_cast<int*>(s_s + LM_ROWS * LM_SPAD);      // [32]
   int* row_out = row_pos + LM_ROWS;                                    // [32]: token * heads + head, -1 for none
+  float* corr_s = reinterpret_cast<float*>(row_out + LM_ROWS);         // [32]
+  float* m_s = corr_s + LM_ROWS;                                       // [32]
+  float* l_s = m_s + LM_ROWS;                                          // [32]
+  __nv_bfloat16* p_s = reinterpret_cast<__nv_bfloat16*>(l_s + LM_ROWS);  // [32][LM_PPAD]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = warp >> 2, cq = warp & 3, g = lane >> 2, t4 = lane & 3;
@@ -360,13 +369,12 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
     }
   };
 
-  float acc[LM_MAXNT][4];
+  float acc[NTQ][4];
 #pragma unroll
-  for (int i = 0; i < LM_MAXNT; ++i)
+  for (int i = 0; i < NTQ; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  const int ntq = rank / 32;                          // 8-column tiles of this warp's quarter
+  float m_row = -INFINITY, l_row = 0.f;               // of row rg * 16 + 4 cq + lane / 8 (eight lanes hold a copy)
   const int col_q = cq * (rank / 4);
   const int ksteps = D / 16;
 
@@ -415,74 +423,80 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
       s_s[rb * LM_SPAD + 8 * cq + 2 * t4 + 1] = key + 1 <= pb ? c[3] * scale_log2 : -INFINITY;
     }
     __syncthreads();
+    // online softmax, once a row: warp cq of a row group takes its rows 4 cq .. 4 cq + 3, eight
+    // lanes a row with four keys each; P goes to shared memory as bfloat16, the factor by
+    // which the row's earlier sums shrink beside it
+    if (group_live) {
+      const int row = rg * 16 + 4 * cq + (lane >> 3), c0 = (lane & 7) * 4;
+      const float4 sv = *reinterpret_cast<const float4*>(s_s + row * LM_SPAD + c0);
+      float mx = fmaxf(fmaxf(sv.x, sv.y), fmaxf(sv.z, sv.w));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      const float m_new = fmaxf(m_row, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = exp2f(m_row - m_use);
+      m_row = m_new;
+      const float p0 = exp2f(sv.x - m_use), p1 = exp2f(sv.y - m_use);
+      const float p2 = exp2f(sv.z - m_use), p3 = exp2f(sv.w - m_use);
+      float sum = (p0 + p1) + (p2 + p3);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      l_row = l_row * corr + sum;
+      uint2 packed;
+      packed.x = pack_bf16(p0, p1);
+      packed.y = pack_bf16(p2, p3);
+      *reinterpret_cast<uint2*>(p_s + row * LM_PPAD + c0) = packed;
+      if ((lane & 7) == 0) corr_s[row] = corr;
+    }
+    __syncthreads();
     if (!group_live) {
       buf ^= 1;
       continue;
     }
-    // online softmax over the row group's 16 x 32 scores, then P V for this warp's columns
+    // P V for this warp's quarter of the columns
     uint32_t pfrag[2][4];
     {
-      float p[2][8];
-      float mx[2] = {-INFINITY, -INFINITY};
+      const __nv_bfloat16* pbase = p_s + (rg * 16 + (lane & 15)) * LM_PPAD + (lane >> 4) * 8;
+      ldmatrix_x4(pfrag[0], pbase);
+      ldmatrix_x4(pfrag[1], pbase + 16);
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const float* srow = s_s + (rg * 16 + g + 8 * r) * LM_SPAD + 2 * t4;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          p[r][2 * j] = srow[8 * j];
-          p[r][2 * j + 1] = srow[8 * j + 1];
-          mx[r] = fmaxf(mx[r], fmaxf(p[r][2 * j], p[r][2 * j + 1]));
-        }
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(m[r], mx[r]);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float corr = exp2f(m[r] - m_use);
-        m[r] = m_new;
-        float sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          p[r][j] = exp2f(p[r][j] - m_use);
-          sum += p[r][j];
-        }
-        l[r] = l[r] * corr + sum;
+        const float corr = corr_s[rg * 16 + g + 8 * r];
         if (corr != 1.f) {                 // the maximum moved: rare once a row has seen a few tiles
 #pragma unroll
-          for (int nt = 0; nt < LM_MAXNT; ++nt)
-            if (nt < ntq) {
-              acc[nt][2 * r] *= corr;
-              acc[nt][2 * r + 1] *= corr;
-            }
+          for (int nt = 0; nt < NTQ; ++nt) {
+            acc[nt][2 * r] *= corr;
+            acc[nt][2 * r + 1] *= corr;
+          }
         }
-      }
-      // columns 2 t4 + 8 j of the 32 keys: j = 0, 1 belong to keys 0..15, j = 2, 3 to 16..31
-#pragma unroll
-      for (int kk = 0; kk < 2; ++kk) {
-        pfrag[kk][0] = pack_bf16(p[0][4 * kk], p[0][4 * kk + 1]);
-        pfrag[kk][1] = pack_bf16(p[1][4 * kk], p[1][4 * kk + 1]);
-        pfrag[kk][2] = pack_bf16(p[0][4 * kk + 2], p[0][4 * kk + 3]);
-        pfrag[kk][3] = pack_bf16(p[1][4 * kk + 2], p[1][4 * kk + 3]);
       }
     }
 #pragma unroll
     for (int kk = 0; kk < 2; ++kk) {
       const __nv_bfloat16* vbase = kt_s + (16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7)) * RS + col_q + (lane >> 4) * 8;
 #pragma unroll
-      for (int dp = 0; dp < LM_MAXNT / 2; ++dp)
-        if (2 * dp < ntq) {
-          uint32_t r4[4];
-          ldmatrix_x4_trans(r4, vbase + 16 * dp);
-          mma_bf16(acc[2 * dp], pfrag[kk], r4[0], r4[1]);
-          if (2 * dp + 1 < ntq) mma_bf16(acc[2 * dp + 1], pfrag[kk], r4[2], r4[3]);
-        }
+      for (int dp = 0; dp < (NTQ + 1) / 2; ++dp) {
+        uint32_t r4[4];
+        ldmatrix_x4_trans(r4, vbase + 16 * dp);
+        mma_bf16(acc[2 * dp], pfrag[kk], r4[0], r4[1]);
+        if (2 * dp + 1 < NTQ) mma_bf16(acc[2 * dp + 1], pfrag[kk], r4[2], r4[3]);
+      }
     }
     buf ^= 1;
   }
   cp_async_wait<0>();
+  if ((lane & 7) == 0) {
+    m_s[rg * 16 + 4 * cq + (lane >> 3)] = m_row;
+    l_s[rg * 16 + 4 * cq + (lane >> 3)] = l_row;
+  }
+  __syncthreads();
+  float m[2], l[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    m[r] = m_s[rg * 16 + g + 8 * r];
+    l[r] = l_s[rg * 16 + g + 8 * r];
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -492,15 +506,14 @@ latent_attention_mma_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
       const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
       __nv_bfloat16* dst = out + (size_t)row * rank + col_q + 2 * t4;
 #pragma unroll
-      for (int nt = 0; nt < LM_MAXNT; ++nt)
-        if (nt < ntq)
-          *reinterpret_cast<__nv_bfloat162*>(dst + 8 * nt) =
-              __floats2bfloat162_rn(acc[nt][2 * r] * inv, acc[nt][2 * r + 1] * inv);
+      for (int nt = 0; nt < NTQ; ++nt)
+        *reinterpret_cast<__nv_bfloat162*>(dst + 8 * nt) =
+            __floats2bfloat162_rn(acc[nt][2 * r] * inv, acc[nt][2 * r + 1] * inv);
     } else {
       float* dst = part_acc + ((size_t)row * n_splits + split) * rank + col_q + 2 * t4;
 #pragma unroll
-      for (int nt = 0; nt < LM_MAXNT; ++nt)
-        if (nt < ntq) *reinterpret_cast<float2*>(dst + 8 * nt) = make_float2(acc[nt][2 * r], acc[nt][2 * r + 1]);
+      for (int nt = 0; nt < NTQ; ++nt)
+        *reinterpret_cast<float2*>(dst + 8 * nt) = make_float2(acc[nt][2 * r], acc[nt][2 * r + 1]);
       if (cq == 0 && t4 == 0) {
         part_ml[((size_t)row * n_splits + split) * 2] = m[r];
         part_ml[((size_t)row * n_splits + split) * 2 + 1] = l[r];
@@ -548,24 +561,35 @@ HB_EXPORT int hb_latent_attention_mma(void* out, float* part_acc, float* part_ml
       n_splits > 65535 || (n_splits > 1 && (part_acc == nullptr || part_ml == nullptr)))
     return HB_BAD_ARGUMENT;
   const int RS = rank + rot + 8;
-  const size_t smem = (size_t)3 * LM_ROWS * RS * 2 + (size_t)LM_ROWS * LM_SPAD * 4 + 2 * LM_ROWS * 4;
+  const size_t smem = (size_t)3 * LM_ROWS * RS * 2 + (size_t)LM_ROWS * LM_SPAD * 4 + 5 * LM_ROWS * 4 +
+                      (size_t)LM_ROWS * LM_PPAD * 2;
   if (smem > 220 * 1024) return HB_BAD_ARGUMENT;
-  static size_t smem_set = 0;
-  if (smem > 48 * 1024 && smem > smem_set) {
-    if (cudaFuncSetAttribute(latent_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
-      return HB_LAUNCH_FAILED;
-    smem_set = smem;
-  }
   const int head_groups = (heads + heads_per_block - 1) / heads_per_block;
   int page_shift = -1;                               // log2 of a page size that is a power of two
   for (int b = 0; b < 31; ++b)
     if ((1 << b) == page_size) page_shift = b;
-  hb_launch(latent_attention_mma_kernel, dim3(n_tiles, head_groups, n_splits), dim3(256), smem, stream,
-            (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q_lat, ql_t, ql_h,
-            (const __nv_bfloat16*)q_rot, qr_t, qr_h, (const __nv_bfloat16*)pages, block_table, bt_stride,
-            q_tiles, cu_tokens, start_pos, heads, heads_per_block, tokens_per_tile, rank, rot, page_size,
-            page_shift, scale * 1.4426950408889634f, n_splits);
+  static size_t smem_set[LM_MAXNT + 1] = {};
+#define HB_LM_LAUNCH(N)                                                                              \
+  case N:                                                                                            \
+    if (smem > 48 * 1024 && smem > smem_set[N]) {                                                    \
+      if (cudaFuncSetAttribute(latent_attention_mma_kernel<N>,                                       \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+        return HB_LAUNCH_FAILED;                                                                     \
+      smem_set[N] = smem;                                                                            \
+    }                                                                                                \
+    hb_launch(latent_attention_mma_kernel<N>, dim3(n_tiles, head_groups, n_splits), dim3(256), smem, \
+              stream, (__nv_bfloat16*)out, part_acc, part_ml, (const __nv_bfloat16*)q_lat, ql_t, ql_h, \
+              (const __nv_bfloat16*)q_rot, qr_t, qr_h, (const __nv_bfloat16*)pages, block_table,     \
+              bt_stride, q_tiles, cu_tokens, start_pos, heads, heads_per_block, tokens_per_tile, rank, \
+              rot, page_size, page_shift, scale * 1.4426950408889634f, n_splits);                    \
+    break;
+  switch (rank / 32) {
+    HB_LM_LAUNCH(1) HB_LM_LAUNCH(2) HB_LM_LAUNCH(3) HB_LM_LAUNCH(4) HB_LM_LAUNCH(5) HB_LM_LAUNCH(6)
+    HB_LM_LAUNCH(7) HB_LM_LAUNCH(8) HB_LM_LAUNCH(9) HB_LM_LAUNCH(10) HB_LM_LAUNCH(11) HB_LM_LAUNCH(12)
+    HB_LM_LAUNCH(13) HB_LM_LAUNCH(14) HB_LM_LAUNCH(15) HB_LM_LAUNCH(16)
+    default: return HB_BAD_ARGUMENT;
+  }
+#undef HB_LM_LAUNCH
   if (n_splits > 1) {
     const int n_rows = n_tokens * heads;
     hb_launch(latent_attention_merge_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream,
