@@ -1342,10 +1342,12 @@ def moe_topk(logits: torch.Tensor, top: int):
     return ids, weights
 
 
-#: bfloat16 steps of more than this many tokens run the experts as two grouped matrix products
+#: bfloat16 steps of at least this many tokens run the experts as two grouped matrix products
 #: of the library (tensor cores; rows sorted by expert on the device, no host round trip, so
-#: the step stays capturable); up to it, and in float32, every (token, choice) pair streams its
-#: expert's rows once, which is what a step of few tokens is bound by
+#: the step stays capturable): every step, since with one block a (token, choice) pair the
+#: streaming kernel took 2 ms a layer for 8 tokens at 16 experts of 2,048 x 1,024 where the
+#: grouped path takes 0.1.  Float32, and inner sizes or widths that are no multiple of 8,
+#: stream every pair's expert rows.
 MOE_GROUPED_MIN_TOKENS = 1
 
 
