@@ -38,10 +38,13 @@ class _StepGraph:
         self.ctx = context_from_views(self.layout, self.dev, [], model.dtype, model.device,
                                       1 if self.decode else num_tokens, core.graph_max_context)
         from ..csrc import ops
-        if self.decode:
+        # the context slices of decode attention over keys and values (a cache with one plane of
+        # rows belongs to a part that cuts its key range itself)
+        kv_specs = [s for s in cache.specs if s.planes == 2]
+        if self.decode and kv_specs:
             self.ctx.extras["decode_splits"] = ops.decode_splits(
-                num_seqs, max(s.num_kv_heads for s in cache.specs) if cache.specs else 1,
-                core.graph_max_context, max(s.head_dim for s in cache.specs) if cache.specs else 128)
+                num_seqs, max(s.num_kv_heads for s in kv_specs), core.graph_max_context,
+                max(s.head_dim for s in kv_specs))
         self.ctx.extras["tile_provider"] = self._tiles
         self._tile_buffers = {}          # (tile, longest first) -> (pinned rows, device rows)
         self._rows_kept = {}             # block-table rows of the staging buffer that are still right
