@@ -47,8 +47,15 @@ def bytes_per_page(plan: ModelPlan, page_size: int, dtype_bytes: int) -> List[in
     counts = [0] * len(specs)
     for g, _ in where.values():
         counts[g] += 1
-    return [s.planes * counts[g] * page_size * s.num_kv_heads * s.head_dim * dtype_bytes
+    return [counts[g] * page_size * s.num_kv_heads * _values_per_head(s) * dtype_bytes
             for g, s in enumerate(specs)]
+
+
+def _values_per_head(spec: PagedCacheSpec) -> int:
+    """Values a token stores per KV head over all planes."""
+    if spec.planes == 2 and spec.value_dim not in (None, spec.head_dim):
+        return spec.head_dim + spec.value_dim
+    return spec.planes * spec.head_dim
 
 
 def pool_sizes_for_bytes(plan: ModelPlan, page_size: int, dtype_bytes: int, kv_cache_bytes: int,
@@ -104,12 +111,22 @@ class KVCacheManager(CacheLayout):
         for g, _ in where.values():
             counts[g] += 1
         self.storage: List[torch.Tensor] = []
+        # groups whose values have another size than their keys keep them in a tensor of their
+        # own: [ids, pages + 1, kv heads, page_size, value_dim]
+        self.value_storage: Dict[int, torch.Tensor] = {}
         for g, spec in enumerate(specs):
             # one page more than the pool hands out: padding rows of captured graphs write there
-            shape = (counts[g], spec.planes, num_pages[g] + 1, spec.num_kv_heads, page_size, spec.head_dim)
+            split = spec.planes == 2 and spec.value_dim not in (None, spec.head_dim)
+            shape = (counts[g], 1 if split else spec.planes, num_pages[g] + 1, spec.num_kv_heads,
+                     page_size, spec.head_dim)
             t = torch.empty(shape, dtype=dtype, device=self.device)
             t.fill_(poison) if poison is not None else t.zero_()
             self.storage.append(t)
+            if split:
+                v = torch.empty((counts[g], num_pages[g] + 1, spec.num_kv_heads, page_size, spec.value_dim),
+                                dtype=dtype, device=self.device)
+                v.fill_(poison) if poison is not None else v.zero_()
+                self.value_storage[g] = v
         # fixed-size state per request slot, for the mixers that keep one; one row more than
         # there are slots: the padding requests of captured steps read and write that one
         self.pad_slot = max_slots
@@ -143,7 +160,9 @@ class KVCacheManager(CacheLayout):
                 return None
             g, idx = self._where[cid]
             planes = self.storage[g][idx]
-            view = LayerCache(planes[0], planes[1] if planes.shape[0] > 1 else None, g,
+            values = self.value_storage[g][idx] if g in self.value_storage else \
+                (planes[1] if planes.shape[0] > 1 else None)
+            view = LayerCache(planes[0], values, g,
                               self.page_size, write=self.plan.schedule[entry].writes_cache)
             self._views[entry] = view
         return view
@@ -166,4 +185,4 @@ class KVCacheManager(CacheLayout):
         return slot
 
     def nbytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.storage)
+        return sum(t.numel() * t.element_size() for t in list(self.storage) + list(self.value_storage.values()))

@@ -5,6 +5,11 @@
 // window and 0 without, wherever the pages lie
 // (python/helios/exec/paged_attn.py:264-295, 368-408; GQA mapping :248-261).
 //
+// Options, each off by default: values of another size than the keys (`vd`); a bias on the
+// score that grows with the distance, score - slopes[h] * (p - j); a sink in the softmax, a
+// key of score 0 without a value, so that the weights are exp(s_j) / (1 + sum exp(s_j)); a
+// gate per (token, head), the head's output times sigmoid(gate[t, h]).
+//
 // Scores, softmax and the weighted sum are float32.  The keys are walked in
 // runs of 32 from `lo`, so the order of every sum depends on the token's
 // position alone: not on how the request was cut into steps, nor on the rest of
@@ -19,8 +24,9 @@ __global__ void attention_generic_kernel(
     T* __restrict__ out, const T* __restrict__ q, int q_stride,
     const T* __restrict__ k_pages, const T* __restrict__ v_pages,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ seq_of_token,
-    const int* __restrict__ positions, int n_rows, int nh, int nkv, int hd, int page_size,
-    int window, float scale) {
+    const int* __restrict__ positions, int n_rows, int nh, int nkv, int hd, int vd, int page_size,
+    int window, float scale, const float* __restrict__ slopes, int sink,
+    const T* __restrict__ gate, int gate_stride) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float q_smem[ATTN_WARPS][ATTN_MAX_HD];
@@ -43,6 +49,7 @@ __global__ void attention_generic_kernel(
 #pragma unroll
   for (int i = 0; i < ND; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
+  const float slope = slopes ? slopes[h] : 0.f;
 
   for (int base = lo; base <= pos; base += 32) {
     const int key = base + lane;
@@ -54,7 +61,7 @@ __global__ void attention_generic_kernel(
       const T* kr = k_pages + (((size_t)page * nkv + kvh) * page_size + key % page_size) * hd;
       float dot = 0.f;
       for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kr[d]), dot);
-      score = dot * scale;
+      score = dot * scale - slope * (float)(pos - key);
     }
     const float m_new = fmaxf(m, warp_max(score));
     const float p = valid ? expf(score - m_new) : 0.f;
@@ -67,36 +74,47 @@ __global__ void attention_generic_kernel(
     for (int j = 0; j < n_valid; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const int pagej = __shfl_sync(0xffffffffu, page, j);
-      const T* vr = v_pages + (((size_t)pagej * nkv + kvh) * page_size + (base + j) % page_size) * hd;
+      const T* vr = v_pages + (((size_t)pagej * nkv + kvh) * page_size + (base + j) % page_size) * vd;
 #pragma unroll
       for (int i = 0; i < ND; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
+        if (d < vd) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
       }
     }
   }
-  const float inv = 1.f / l;
-  T* orow = out + (size_t)t * nh * hd + (size_t)h * hd;
+  if (sink) {                       // the key of score 0: it adds exp(0 - m) to the sum only
+    const float m_new = fmaxf(m, 0.f);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(-m_new);
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acc[i] *= corr;
+  }
+  float inv = 1.f / l;
+  if (gate) inv /= 1.f + expf(-to_float(gate[(size_t)t * gate_stride + h]));
+  T* orow = out + (size_t)t * nh * vd + (size_t)h * vd;
 #pragma unroll
   for (int i = 0; i < ND; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) orow[d] = from_float<T>(acc[i] * inv);
+    if (d < vd) orow[d] = from_float<T>(acc[i] * inv);
   }
 }
 
 HB_EXPORT int hb_attention_generic(void* out, const void* q, int q_stride, const void* k_pages,
                                    const void* v_pages, const int* block_table, int bt_stride,
                                    const int* seq_of_token, const int* positions, int T, int nh,
-                                   int nkv, int hd, int page_size, int window, float scale,
-                                   int act_dt, cudaStream_t stream) {
+                                   int nkv, int hd, int vd, int page_size, int window, float scale,
+                                   const float* slopes, int sink, const void* gate,
+                                   int gate_stride, int act_dt, cudaStream_t stream) {
   if (T <= 0) return HB_OK;
-  if (hd <= 0 || hd > ATTN_MAX_HD || nkv <= 0 || nh % nkv != 0 || page_size <= 0)
+  if (hd <= 0 || hd > ATTN_MAX_HD || vd <= 0 || vd > ATTN_MAX_HD || nkv <= 0 || nh % nkv != 0 ||
+      page_size <= 0)
     return HB_BAD_ARGUMENT;
   const int n_rows = T * nh;
   const int blocks = (n_rows + ATTN_WARPS - 1) / ATTN_WARPS;
   HB_DISPATCH_DTYPE(act_dt, TA,
     hb_launch(attention_generic_kernel<TA>, dim3(blocks), dim3(ATTN_WARPS * 32), 0, stream, 
         (TA*)out, (const TA*)q, q_stride, (const TA*)k_pages, (const TA*)v_pages, block_table,
-        bt_stride, seq_of_token, positions, n_rows, nh, nkv, hd, page_size, window, scale));
+        bt_stride, seq_of_token, positions, n_rows, nh, nkv, hd, vd, page_size, window, scale,
+        slopes, sink, (const TA*)gate, gate_stride));
   return hb_check_launch();
 }

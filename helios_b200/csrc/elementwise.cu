@@ -494,3 +494,195 @@ HB_EXPORT int hb_rmsnorm_add(float* residual, const void* y, const float* weight
                 weight, (TC*)copy, H, eps)));
   return hb_check_launch();
 }
+
+// ---------------------------------------------------------------- layer norm with a pending sum
+// A block whose sublayers all read ONE norm of the stream leaves its outputs to be added:
+//   residual[r, c] += mult * (sa[c] * a[r, c] + sb[c] * b[r, c])      (float32; a, b, sa, sb optional)
+// and the norm that meets the stream next does the add and norms the new row:
+//   out[i, c] = (x[c] - mean) * rsqrt(mean((x - mean)^2) + eps) * w[c] + bias[c],   x = residual[r]
+// with r = rows ? rows[i] : i.  With `rows` the residual is not written back (the final norm
+// runs on the wanted rows only); with `out` null only the add is done.  The row lies in shared
+// memory between the passes; mean and variance are two passes over it in float32.
+template <typename TA>
+__global__ void __launch_bounds__(NORM_THREADS)
+add_layernorm_kernel(TA* __restrict__ out, float* __restrict__ residual, const TA* __restrict__ a,
+                     const float* __restrict__ sa, const TA* __restrict__ b,
+                     const float* __restrict__ sb, float mult, const float* __restrict__ weight,
+                     const float* __restrict__ bias, const int* __restrict__ rows, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row_sm[];
+  __shared__ float scratch[33];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* res = residual + (size_t)r * H;
+  const TA* ar = a ? a + (size_t)r * H : nullptr;
+  const TA* br = b ? b + (size_t)r * H : nullptr;
+  const bool write_back = (rows == nullptr) && (ar != nullptr || br != nullptr);
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float v = res[c];
+    float add = 0.f;
+    if (ar) add = (sa ? sa[c] : 1.f) * to_float(ar[c]);
+    if (br) add = fmaf(sb ? sb[c] : 1.f, to_float(br[c]), add);
+    if (ar || br) v = fmaf(mult, add, v);
+    if (write_back) res[c] = v;
+    row_sm[c] = v;
+    sum += v;
+  }
+  if (out == nullptr) return;
+  const float mean = block_sum(sum, scratch) / (float)H;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float d = row_sm[c] - mean;
+    sq = fmaf(d, d, sq);
+  }
+  const float rstd = rsqrtf(block_sum(sq, scratch) / (float)H + eps);
+  TA* o = out + (size_t)i * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float y = (row_sm[c] - mean) * rstd * weight[c];
+    if (bias) y += bias[c];
+    o[c] = from_float<TA>(y);
+  }
+}
+
+HB_EXPORT int hb_add_layernorm(void* out, float* residual, const void* a, const float* sa,
+                               const void* b, const float* sb, float mult, const float* weight,
+                               const float* bias, const int* rows, int n_out, int H, float eps,
+                               int act_dt, cudaStream_t stream) {
+  if (n_out <= 0) return HB_OK;
+  const size_t smem = (size_t)H * sizeof(float);
+  if (H <= 0 || smem > 200 * 1024) return HB_BAD_ARGUMENT;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    if (smem > 40 * 1024)
+      cudaFuncSetAttribute(add_layernorm_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    hb_launch(add_layernorm_kernel<TA>, dim3(n_out), dim3(NORM_THREADS), smem, stream, (TA*)out, residual,
+              (const TA*)a, sa, (const TA*)b, sb, mult, weight, bias, rows, H, eps));
+  return hb_check_launch();
+}
+
+// ---------------------------------------------------------------- learned positions
+// hidden[t, :] (f32) += table[index[t], :]: a vector per position, added to the embedded token.
+template <typename T>
+__global__ void add_table_rows_kernel(float* __restrict__ hidden, const T* __restrict__ table,
+                                      const int* __restrict__ index, int H, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int id = index[t];
+  if (id < 0 || id >= V) id = V - 1;      // positions are bounded on the host
+  const T* row = table + (size_t)id * H;
+  float* o = hidden + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] += to_float(row[i]);
+}
+
+HB_EXPORT int hb_add_table_rows(float* hidden, const void* table, const int* index, int T, int H,
+                                int V, int table_dt, cudaStream_t stream) {
+  if (T <= 0) return HB_OK;
+  HB_DISPATCH_DTYPE(table_dt, TT,
+    hb_launch(add_table_rows_kernel<TT>, dim3(T), dim3(256), 0, stream, hidden, (const TT*)table, index, H, V));
+  return hb_check_launch();
+}
+
+// ---------------------------------------------------------------- float32 rows into wider act rows
+// dst[t, col0 + c] = src[t, c] in the activation dtype (dst has `ld` columns): puts the stream
+// beside another tensor as the input of one product.
+template <typename T>
+__global__ void cast_rows_kernel(T* __restrict__ dst, int ld, int col0, const float* __restrict__ src,
+                                 int W, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / W;
+    const int c = (int)(idx - t * W);
+    dst[t * ld + col0 + c] = from_float<T>(src[idx]);
+  }
+}
+
+HB_EXPORT int hb_cast_rows(void* dst, int ld, int col0, const float* src, int T, int W, int act_dt,
+                           cudaStream_t stream) {
+  if (T <= 0) return HB_OK;
+  if (W <= 0 || col0 < 0 || col0 + W > ld) return HB_BAD_ARGUMENT;
+  const size_t total = (size_t)T * W;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(cast_rows_kernel<TA>, dim3((unsigned)blocks), dim3(256), 0, stream, (TA*)dst, ld, col0, src, W, total));
+  return hb_check_launch();
+}
+
+// ---------------------------------------------------------------- q/k norm + cache write
+// rows: [T, ld] with q heads (nh * hd), k heads (nkv * hd), v heads (nkv * vd) from column 0.
+// One warp per (token, head): a q head becomes q / rms(q) * wq * temp(pos) in place, with
+//   temp(p) = 1 + coef * ln(floor((p + 1) / every) + 1)        (every > 0; else 1)
+// a k head becomes k / rms(k) * wk at the token's place in its key pages, a v head is copied
+// to the value pages.  rms over the head's hd values with eps inside the root; norm weights
+// null: no norm.  Pages: [page, kv head, slot, hd] and [page, kv head, slot, vd].  All
+// arithmetic float32.  Without `write_cache` k is normed in place and v left alone.
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_norm_kv_write_kernel(T* __restrict__ rows, int ld, const int* __restrict__ positions,
+                        const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                        int bt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens,
+                        int nh, int nkv, int hd, int vd, const float* __restrict__ wq,
+                        const float* __restrict__ wk, float eps, float coef, int every,
+                        int page_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_token = nh + 2 * nkv;
+  const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (item >= (long)n_tokens * per_token) return;
+  const int t = (int)(item / per_token), h = (int)(item - (long)t * per_token);
+  const int pos = positions[t];
+  T* row = rows + (size_t)t * ld;
+  size_t page_base = 0;
+  int slot = 0;
+  if (write_cache && h >= nh) {
+    const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+    slot = pos % page_size;
+    page_base = (size_t)page * nkv;
+  }
+  if (h >= nh + nkv) {                       // a value head
+    if (!write_cache) return;
+    const int g = h - nh - nkv;
+    const T* src = row + (size_t)(nh + nkv) * hd + (size_t)g * vd;
+    T* dst = v_pages + ((page_base + g) * page_size + slot) * vd;
+    for (int d = lane; d < vd; d += 32) dst[d] = src[d];
+    return;
+  }
+  const bool is_q = h < nh;
+  T* x = row + (size_t)h * hd;
+  const float* w = is_q ? wq : wk;
+  float ss = 0.f;
+  for (int d = lane; d < hd; d += 32) { const float v = to_float(x[d]); ss = fmaf(v, v, ss); }
+  float f = 1.f;
+  if (w) f = rsqrtf(warp_sum(ss) / (float)hd + eps);
+  float temp = 1.f;
+  if (is_q && every > 0) temp = 1.f + coef * logf((float)((pos + 1) / every) + 1.f);
+  T* dst = x;
+  if (!is_q && write_cache) dst = k_pages + ((page_base + (h - nh)) * page_size + slot) * hd;
+  for (int d = lane; d < hd; d += 32) {
+    float v = to_float(x[d]) * f;
+    if (w) v *= w[d];
+    dst[d] = from_float<T>(v * temp);
+  }
+}
+
+HB_EXPORT int hb_qk_norm_kv_write(void* rows, int ld, const int* positions, const int* seq_of_token,
+                                  const int* block_table, int bt_stride, void* k_pages, void* v_pages,
+                                  int T, int nh, int nkv, int hd, int vd, const float* wq,
+                                  const float* wk, float eps, float coef, int every, int page_size,
+                                  int write_cache, int act_dt, cudaStream_t stream) {
+  if (T <= 0) return HB_OK;
+  if (nh <= 0 || nkv <= 0 || hd <= 0 || vd <= 0 || page_size <= 0 || every < 0 ||
+      (long)nh * hd + (long)nkv * (hd + vd) > ld)
+    return HB_BAD_ARGUMENT;
+  const long items = (long)T * (nh + 2 * nkv);
+  HB_DISPATCH_DTYPE(act_dt, TA,
+    hb_launch(qk_norm_kv_write_kernel<TA>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (TA*)rows, ld,
+              positions, seq_of_token, block_table, bt_stride, (TA*)k_pages, (TA*)v_pages, T, nh, nkv,
+              hd, vd, wq, wk, eps, coef, every, page_size, write_cache));
+  return hb_check_launch();
+}

@@ -10,40 +10,63 @@
 // are read about once); `moe_combine` adds a token's choices in the order of the choice.
 // The gate is the clamped form of `glu_value` in elementwise.cu:
 // g' = min(g, limit), u' = clamp(u, -limit, limit), y = g' sigmoid(1.702 g') (u' + 1).
+//
+// The same kernels serve a second form, chosen by arguments: s = softmax(z) over all router
+// outputs; the choice goes by s + correction (a vector the checkpoint brings) while the weight
+// stays s; the weight multiplies the expert's OUTPUT; the gate is silu; router outputs from
+// `n_real` on stand for experts without tensors that return their input; and a tensor
+// `base` (an expert every token runs) is added to the sum.
 #include "common.cuh"
 
 constexpr int MOE_MAX_TOP = 16;
+enum { MOE_SIGMOID = 0, MOE_SOFTMAX = 1 };
+enum { MOE_GATE_SILU = 0, MOE_GATE_CLAMPED_SWISH = 2 };     // the codes of the gated activations
 
 __global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weights,
-                                const float* __restrict__ logits, int n_tokens, int experts,
-                                int top) {
+                                const float* __restrict__ logits,
+                                const float* __restrict__ correction, int n_tokens, int experts,
+                                int top, int kind) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_tokens) return;
   const float* z = logits + (size_t)t * experts;
+  // softmax: the scores need the row's maximum and sum (float32, experts in their order)
+  float zmax = 0.f, denom = 1.f;
+  if (kind == MOE_SOFTMAX) {
+    zmax = -INFINITY;
+    for (int e = 0; e < experts; ++e) zmax = fmaxf(zmax, z[e]);
+    denom = 0.f;
+    for (int e = 0; e < experts; ++e) denom += expf(z[e] - zmax);
+  }
+  // sigmoid scores without a correction are ordered as z is, which does not saturate
+  const bool by_logit = (kind == MOE_SIGMOID) && (correction == nullptr);
   int chosen[MOE_MAX_TOP];
   for (int k = 0; k < top; ++k) {
-    float best = 0.f;
+    float best = 0.f, best_score = 0.f;
     int at = -1;
     for (int e = 0; e < experts; ++e) {
       bool taken = false;
       for (int j = 0; j < k; ++j) taken |= (chosen[j] == e);
       if (taken) continue;
-      if (at < 0 || z[e] > best) { best = z[e]; at = e; }     // a NaN never wins: `at` stays valid
+      const float s = (kind == MOE_SOFTMAX) ? expf(z[e] - zmax) / denom : 1.f / (1.f + expf(-z[e]));
+      const float c = by_logit ? z[e] : s + (correction ? correction[e] : 0.f);
+      if (at < 0 || c > best) { best = c; best_score = s; at = e; }   // a NaN never wins: `at` stays valid
     }
     chosen[k] = at;
     ids[(size_t)t * top + k] = at;
-    weights[(size_t)t * top + k] = 1.f / (1.f + expf(-best));
+    weights[(size_t)t * top + k] = best_score;
   }
 }
 
-HB_EXPORT int hb_moe_topk(int* ids, float* weights, const float* logits, int n_tokens, int experts,
-                          int top, cudaStream_t stream) {
+HB_EXPORT int hb_moe_topk(int* ids, float* weights, const float* logits, const float* correction,
+                          int n_tokens, int experts, int top, int kind, cudaStream_t stream) {
   if (n_tokens <= 0) return HB_OK;
-  if (experts <= 0 || top <= 0 || top > experts || top > MOE_MAX_TOP) return HB_BAD_ARGUMENT;
+  if (experts <= 0 || top <= 0 || top > experts || top > MOE_MAX_TOP ||
+      (kind != MOE_SIGMOID && kind != MOE_SOFTMAX))
+    return HB_BAD_ARGUMENT;
   hb_launch(moe_topk_kernel, dim3((n_tokens + 127) / 128), dim3(128), 0, stream, ids, weights,
-            logits, n_tokens, experts, top);
+            logits, correction, n_tokens, experts, top, kind);
   return hb_check_launch();
 }
 
@@ -54,7 +77,7 @@ __global__ void __launch_bounds__(256)
 moe_expert_rows_kernel(float* __restrict__ partial, const T* __restrict__ h,
                        const T* __restrict__ w_gate_up, const T* __restrict__ w_down,
                        const int* __restrict__ ids, const float* __restrict__ weights, int top,
-                       int width, int ff, float limit) {
+                       int width, int ff, float limit, int gate_kind, int weight_output, int n_real) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float sm[];
@@ -65,9 +88,15 @@ moe_expert_rows_kernel(float* __restrict__ partial, const T* __restrict__ h,
   const float w = weights[pair];
   const int t = pair / top;
   const T* hr = h + (size_t)t * width;
+  float* dst = partial + (size_t)pair * width;
+  if (e >= n_real) {               // an expert without tensors: its output is its input
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = w * to_float(hr[c]);
+    return;
+  }
+  const float w_in = weight_output ? 1.f : w, w_out = weight_output ? w : 1.f;
   // the expert's input, rounded as the activation dtype rounds it
   for (int c = threadIdx.x; c < width; c += blockDim.x)
-    x[c] = to_float(from_float<T>(w * to_float(hr[c])));
+    x[c] = to_float(from_float<T>(w_in * to_float(hr[c])));
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   const T* wg = w_gate_up + (size_t)e * 2 * ff * width;
@@ -82,29 +111,37 @@ moe_expert_rows_kernel(float* __restrict__ partial, const T* __restrict__ h,
     g = warp_sum(g);
     u = warp_sum(u);
     if (lane == 0) {
-      g = fminf(to_float(from_float<T>(g)), limit);
-      u = fminf(fmaxf(to_float(from_float<T>(u)), -limit), limit);
-      y[f] = to_float(from_float<T>(g / (1.f + expf(-1.702f * g)) * (u + 1.f)));
+      g = to_float(from_float<T>(g));
+      u = to_float(from_float<T>(u));
+      if (gate_kind == MOE_GATE_SILU) {
+        y[f] = to_float(from_float<T>(g / (1.f + expf(-g)) * u));
+      } else {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        y[f] = to_float(from_float<T>(g / (1.f + expf(-1.702f * g)) * (u + 1.f)));
+      }
     }
   }
   __syncthreads();
   const T* wd = w_down + (size_t)e * width * ff;
-  float* dst = partial + (size_t)pair * width;
   for (int c = warp; c < width; c += n_warps) {
     const T* dr = wd + (size_t)c * ff;
     float a = 0.f;
     for (int f = lane; f < ff; f += 32) a = fmaf(to_float(dr[f]), y[f], a);
     a = warp_sum(a);
-    if (lane == 0) dst[c] = a;
+    if (lane == 0) dst[c] = w_out * a;
   }
 }
 
 HB_EXPORT int hb_moe_expert_rows(float* partial, const void* h, const void* w_gate_up,
                                  const void* w_down, const int* ids, const float* weights,
-                                 int n_tokens, int top, int width, int ff, float limit, int act_dt,
+                                 int n_tokens, int top, int width, int ff, float limit,
+                                 int gate_kind, int weight_output, int n_real, int act_dt,
                                  cudaStream_t stream) {
   if (n_tokens <= 0) return HB_OK;
-  if (top <= 0 || width <= 0 || ff <= 0) return HB_BAD_ARGUMENT;
+  if (top <= 0 || width <= 0 || ff <= 0 || n_real < 0 ||
+      (gate_kind != MOE_GATE_SILU && gate_kind != MOE_GATE_CLAMPED_SWISH))
+    return HB_BAD_ARGUMENT;
   const size_t smem = (size_t)(width + ff) * sizeof(float);
   if (smem > 200 * 1024) return HB_BAD_ARGUMENT;
   HB_DISPATCH_DTYPE(act_dt, TA,
@@ -113,14 +150,14 @@ HB_EXPORT int hb_moe_expert_rows(float* partial, const void* h, const void* w_ga
                            (int)smem);
     hb_launch(moe_expert_rows_kernel<TA>, dim3(n_tokens * top), dim3(256), smem, stream,
               partial, (const TA*)h, (const TA*)w_gate_up, (const TA*)w_down, ids, weights, top, width,
-              ff, limit));
+              ff, limit, gate_kind, weight_output, n_real));
   return hb_check_launch();
 }
 
-// out[t, :] = sum over k of partial[t * top + k, :], k = 0..top-1 in that order
+// out[t, :] = base[t, :] (if given) + sum over k of partial[t * top + k, :], k = 0..top-1 in that order
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ partial,
-                                   size_t total, int width, int top) {
+                                   const T* __restrict__ base, size_t total, int width, int top) {
   pdl_launch_dependents();
   pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -129,19 +166,20 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict_
     const int c = (int)(idx - t * width);
     float a = 0.f;
     for (int k = 0; k < top; ++k) a += partial[(t * top + k) * width + c];
+    if (base) a += to_float(base[idx]);
     out[idx] = from_float<T>(a);
   }
 }
 
-HB_EXPORT int hb_moe_combine(void* out, const float* partial, int n_tokens, int width, int top,
-                             int act_dt, cudaStream_t stream) {
+HB_EXPORT int hb_moe_combine(void* out, const float* partial, const void* base, int n_tokens,
+                             int width, int top, int act_dt, cudaStream_t stream) {
   if (n_tokens <= 0) return HB_OK;
   const size_t total = (size_t)n_tokens * width;
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   HB_DISPATCH_DTYPE(act_dt, TA,
     hb_launch(moe_combine_kernel<TA>, dim3((unsigned)blocks), dim3(256), 0, stream, (TA*)out,
-              partial, total, width, top));
+              partial, (const TA*)base, total, width, top));
   return hb_check_launch();
 }
 
@@ -185,6 +223,7 @@ HB_EXPORT int hb_moe_sort(int* ends, int* place, const int* ids, int n_pairs, in
 }
 
 // rows[place[pair], :] = weight[pair] * h[pair / top, :], rounded to the activation dtype
+// (weights null: the row itself)
 template <typename T>
 __global__ void moe_scatter_rows_kernel(T* __restrict__ rows, const T* __restrict__ h,
                                         const int* __restrict__ place,
@@ -192,9 +231,13 @@ __global__ void moe_scatter_rows_kernel(T* __restrict__ rows, const T* __restric
   pdl_launch_dependents();
   pdl_wait();
   const int pair = blockIdx.x;
-  const float w = weights[pair];
   const T* src = h + (size_t)(pair / top) * width;
   T* dst = rows + (size_t)place[pair] * width;
+  if (weights == nullptr) {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+    return;
+  }
+  const float w = weights[pair];
   for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = from_float<T>(w * to_float(src[c]));
 }
 
@@ -207,25 +250,39 @@ HB_EXPORT int hb_moe_scatter_rows(void* rows, const void* h, const int* place, c
   return hb_check_launch();
 }
 
-// out[t, :] = sum over k = 0..top-1, in that order, of rows[place[t * top + k], :]
+// out[t, :] = base[t, :] + sum over k = 0..top-1, in that order, of w_k * y_k, where y_k is
+// rows[place[t * top + k], :], or h[t, :] itself for a pair whose expert id is n_real or more
+// (an expert without tensors); w_k = weights[t * top + k], or 1 with weights null.  base, ids,
+// weights and h may be null (then: no base, no such experts, no weights).  float32 sums.
 template <typename T>
 __global__ void moe_gather_sum_kernel(T* __restrict__ out, const T* __restrict__ rows,
-                                      const int* __restrict__ place, int top, int width) {
+                                      const int* __restrict__ place, const int* __restrict__ ids,
+                                      const float* __restrict__ weights, const T* __restrict__ h,
+                                      const T* __restrict__ base, int n_real, int top, int width) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float a = 0.f;
-    for (int k = 0; k < top; ++k) a += to_float(rows[(size_t)place[t * top + k] * width + c]);
+    for (int k = 0; k < top; ++k) {
+      const int pair = t * top + k;
+      const bool same = ids != nullptr && ids[pair] >= n_real;
+      const float y = same ? to_float(h[(size_t)t * width + c])
+                           : to_float(rows[(size_t)place[pair] * width + c]);
+      a = weights ? fmaf(weights[pair], y, a) : a + y;
+    }
+    if (base) a += to_float(base[(size_t)t * width + c]);
     out[(size_t)t * width + c] = from_float<T>(a);
   }
 }
 
-HB_EXPORT int hb_moe_gather_sum(void* out, const void* rows, const int* place, int n_tokens, int top,
-                                int width, int act_dt, cudaStream_t stream) {
+HB_EXPORT int hb_moe_gather_sum(void* out, const void* rows, const int* place, const int* ids,
+                                const float* weights, const void* h, const void* base, int n_real,
+                                int n_tokens, int top, int width, int act_dt, cudaStream_t stream) {
   if (n_tokens <= 0) return HB_OK;
+  if (ids != nullptr && h == nullptr) return HB_BAD_ARGUMENT;
   HB_DISPATCH_DTYPE(act_dt, TA,
     hb_launch(moe_gather_sum_kernel<TA>, dim3(n_tokens), dim3(256), 0, stream, (TA*)out,
-              (const TA*)rows, place, top, width));
+              (const TA*)rows, place, ids, weights, (const TA*)h, (const TA*)base, n_real, top, width));
   return hb_check_launch();
 }

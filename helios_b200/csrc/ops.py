@@ -112,6 +112,12 @@ def attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, h
     return tuple(names)
 
 
+def option_attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int,
+                               value_dim: int):
+    """Libraries attention with ``AttentionOptions`` may choose from at these sizes."""
+    return ("attention_generic",)
+
+
 # ------------------------------------------------------------------ embedding
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     """float32 [T, H] rows of ``table`` ([V, H], float32 or bfloat16) at int32 ``ids``."""
@@ -223,12 +229,51 @@ def rope_kv_write(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[
 
 
 # ------------------------------------------------------------------ attention
+class AttentionOptions:
+    """What an attention kernel may be asked for beyond scaled dot products, a causal mask and
+    a window; each is off by default.
+
+    ``slopes``   float32 [heads]: score - slopes[h] * (query position - key position)
+    ``sink``     the softmax has a key of score 0 that carries no value:
+                 weights exp(s_j) / (1 + sum_j exp(s_j))
+    ``gate``     [T, >= heads] in the activation dtype, a view whose rows are ``gate_stride``
+                 apart: head h's output at token t is multiplied by sigmoid(gate[t, h])
+    ``value_dim`` values per head where they differ from the keys' (None: the same)"""
+
+    __slots__ = ("slopes", "sink", "gate", "gate_stride", "value_dim")
+
+    def __init__(self, slopes: Optional[torch.Tensor] = None, sink: bool = False,
+                 gate: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> None:
+        self.slopes, self.sink, self.gate, self.value_dim = slopes, bool(sink), gate, value_dim
+        self.gate_stride = 0 if gate is None else int(gate.stride(0))
+
+    @property
+    def plain(self) -> bool:
+        return self.slopes is None and not self.sink and self.gate is None and self.value_dim is None
+
+    def check(self, tokens: int, num_heads: int, like: torch.Tensor) -> None:
+        if self.slopes is not None:
+            _check(self.slopes, "slopes", torch.float32, 1)
+            if self.slopes.numel() != num_heads:
+                raise KernelError(f"{self.slopes.numel()} slopes for {num_heads} heads")
+        if self.gate is not None:
+            g = self.gate
+            if not g.is_cuda or g.dtype != like.dtype or g.dim() != 2 or g.shape[0] != tokens \
+                    or g.shape[1] < num_heads or g.stride(1) != 1:
+                raise KernelError(f"gate must be [{tokens}, >= {num_heads}] {like.dtype} with unit column stride")
+
+
+_NO_OPTIONS = AttentionOptions()
+
+
 def attention_generic(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_table: torch.Tensor, seq_of_token: torch.Tensor,
                       positions: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                      page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+                      page_size: int, window: Optional[int], scale: float,
+                      options: Optional["AttentionOptions"] = None) -> torch.Tensor:
     """Attention of every token of the batch over its request's pages; q is read from the
-    first ``nh * hd`` columns of ``qkv``.  Returns [T, nh * hd] in qkv's dtype."""
+    first ``nh * hd`` columns of ``qkv``.  Returns [T, nh * vd] in qkv's dtype (vd = hd
+    unless ``options`` says otherwise)."""
     _check(qkv, "qkv", None, 2)
     _check(k_pages, "k_pages", qkv.dtype, 4)
     _check(v_pages, "v_pages", qkv.dtype, 4)
@@ -243,13 +288,21 @@ def attention_generic(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
         raise KernelError(f"k_pages has shape {tuple(k_pages.shape)}, expected "
                           f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
     T = qkv.shape[0]
-    out = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    opt = options or _NO_OPTIONS
+    vd = opt.value_dim or head_dim
+    opt.check(T, num_heads, qkv)
+    if not 0 < vd <= 256 or tuple(v_pages.shape[1:]) != (num_kv_heads, page_size, vd):
+        raise KernelError(f"v_pages has shape {tuple(v_pages.shape)}, expected "
+                          f"[pages, {num_kv_heads}, {page_size}, {vd}] with at most 256 values a head")
+    out = torch.empty((T, num_heads * vd), dtype=qkv.dtype, device=qkv.device)
     f = _fn("attention_generic", "hb_attention_generic",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p,
+             c_int, c_int, c_void_p])
     _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), _p(block_table),
            block_table.shape[1], _p(seq_of_token), _p(positions), T, num_heads, num_kv_heads,
-           head_dim, page_size, int(window or 0), float(scale), _dt(qkv.dtype), _stream()),
+           head_dim, vd, page_size, int(window or 0), float(scale), _p(opt.slopes), int(opt.sink),
+           _p(opt.gate), opt.gate_stride, _dt(qkv.dtype), _stream()),
          "attention_generic")
     return out
 
@@ -1007,7 +1060,7 @@ def _step_tiles(ctx, tile: int, longest_first: bool, device) -> torch.Tensor:
 def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
               page_size: int, window: Optional[int], scale: float,
-              fresh=None) -> torch.Tensor:
+              fresh=None, options: Optional[AttentionOptions] = None) -> torch.Tensor:
     """Attention of the step's tokens over the cache; chooses the kernel by dtype, sizes
     and the shape of the batch described by ``ctx``.  bfloat16 with a tiled head size
     runs on the tensor cores (split-context decode kernel for batches of single tokens,
@@ -1015,7 +1068,12 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
 
     ``fresh`` = (cos, sin, write_cache): ``qkv`` comes straight from the projection; q and k
     are rotated (tables None: no rotation) and, with ``write_cache``, k and v stored in the
-    pages first: inside the decode kernel where that one runs, else by ``rope_kv_write``."""
+    pages first: inside the decode kernel where that one runs, else by ``rope_kv_write``.
+
+    ``options`` (``AttentionOptions``): a distance bias, a sink, a gate, values of another size."""
+    if options is not None and not options.plain:
+        return _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, num_kv_heads,
+                                       head_dim, page_size, window, scale, options)
     decode = (qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS and ctx.decode_only
               and num_heads // num_kv_heads <= 16)
     rotary, write_cache = None, False
@@ -1054,6 +1112,127 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                                       window, scale)
     return attention_generic(qkv, k_pages, v_pages, block_table, ctx.seq_of_token, ctx.positions,
                              num_heads, num_kv_heads, head_dim, page_size, window, scale)
+
+
+def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, num_kv_heads, head_dim,
+                            page_size, window, scale, options: AttentionOptions) -> torch.Tensor:
+    """The kernels that take ``AttentionOptions``; q is ready and the step's keys and values
+    are in the pages (``qk_norm_kv_write``)."""
+    return attention_generic(qkv, k_pages, v_pages, block_table, ctx.seq_of_token, ctx.positions,
+                             num_heads, num_kv_heads, head_dim, page_size, window, scale, options)
+
+
+def qk_norm_kv_write(rows: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                     block_table: torch.Tensor, k_pages: Optional[torch.Tensor],
+                     v_pages: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                     value_dim: int, page_size: int, q_weight: Optional[torch.Tensor],
+                     k_weight: Optional[torch.Tensor], eps: float, temp_coef: float = 0.0,
+                     temp_every: int = 0, write_cache: bool = True) -> None:
+    """For the rows of a fused projection ([T, ld]: q heads, k heads, v heads from column 0,
+    whatever follows): every q head becomes q / rms(q) * q_weight * (1 + temp_coef *
+    ln(floor((p + 1) / temp_every) + 1)) in place (p the token's position; ``temp_every`` 0: no
+    such factor; weights None: no norm), every k head k / rms(k) * k_weight at the token's
+    place in the key pages, every v head goes to the value pages.  float32 arithmetic."""
+    _check(rows, "rows", None, 2)
+    T, ld = rows.shape
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("query and key norm come together")
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _check(w, name, torch.float32, 1)
+            if w.numel() != head_dim:
+                raise KernelError(f"{name} has {w.numel()} entries for heads of {head_dim}")
+    if num_heads * head_dim + num_kv_heads * (head_dim + value_dim) > ld:
+        raise KernelError(f"rows of {ld} columns do not hold {num_heads} q, {num_kv_heads} k and v heads")
+    if write_cache:
+        for name, pages, d in (("k_pages", k_pages, head_dim), ("v_pages", v_pages, value_dim)):
+            _check(pages, name, rows.dtype, 4)
+            if tuple(pages.shape[1:]) != (num_kv_heads, page_size, d):
+                raise KernelError(f"{name} has shape {tuple(pages.shape)}, expected "
+                                  f"[pages, {num_kv_heads}, {page_size}, {d}]")
+    f = _fn("elementwise", "hb_qk_norm_kv_write",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_int,
+             c_void_p])
+    _run(f(_p(rows), ld, _p(positions), _p(seq_of_token), _p(block_table), block_table.shape[1],
+           _p(k_pages) if write_cache else 0, _p(v_pages) if write_cache else 0, T, num_heads,
+           num_kv_heads, head_dim, value_dim, _p(q_weight), _p(k_weight), float(eps), float(temp_coef),
+           int(temp_every), page_size, 1 if write_cache else 0, _dt(rows.dtype), _stream()),
+         "qk_norm_kv_write")
+
+
+# ------------------------------------------------------------------ layer norm, learned positions
+def add_layernorm(residual: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                  eps: float, out_dtype: Optional[torch.dtype], rows: Optional[torch.Tensor] = None,
+                  a: Optional[torch.Tensor] = None, scale_a: Optional[torch.Tensor] = None,
+                  b: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None,
+                  mult: float = 1.0) -> Optional[torch.Tensor]:
+    """``residual += mult * (scale_a * a + scale_b * b)`` (float32, in place; a, b [n, H] in one
+    dtype, the scales float32 [H] or None for 1) and the layer norm of the new rows, (x - mean) /
+    sqrt(var + eps) * weight + bias, in ``out_dtype``.  With ``rows`` (int32) only those rows are
+    normed and the residual is left as it was.  ``out_dtype`` None: only the add."""
+    _check(residual, "residual", torch.float32, 2)
+    n, H = residual.shape
+    act = None
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _check(t, name, None, 2)
+            if tuple(t.shape) != (n, H) or (act is not None and t.dtype != act):
+                raise KernelError(f"{name} {tuple(t.shape)} {t.dtype} does not match residual {(n, H)}")
+            act = t.dtype
+    for name, t in (("scale_a", scale_a), ("scale_b", scale_b), ("weight", weight), ("bias", bias)):
+        if t is not None:
+            _check(t, name, torch.float32, 1)
+            if t.numel() != H:
+                raise KernelError(f"{name} has {t.numel()} entries for width {H}")
+    out = None
+    n_out = n
+    if out_dtype is not None:
+        if weight is None:
+            raise KernelError("a norm needs its weight")
+        if act is not None and act != out_dtype:
+            raise KernelError(f"pending tensors are {act}, the norm's output {out_dtype}")
+        if rows is not None:
+            _check(rows, "rows", torch.int32, 1)
+            n_out = rows.numel()
+        out = torch.empty((n_out, H), dtype=out_dtype, device=residual.device)
+    elif act is None:
+        return None
+    f = _fn("elementwise", "hb_add_layernorm",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _run(f(_p(out), _p(residual), _p(a), _p(scale_a), _p(b), _p(scale_b), float(mult), _p(weight),
+           _p(bias), _p(rows) if out is not None else 0, n_out, H, float(eps),
+           _dt(out_dtype if out_dtype is not None else act), _stream()), "add_layernorm")
+    return out
+
+
+def add_table_rows(hidden: torch.Tensor, table: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """``hidden[t] += table[index[t]]`` in float32 and in place (hidden float32 [T, H], table
+    [V, H] float32 or bfloat16, index int32 [T])."""
+    _check(hidden, "hidden", torch.float32, 2)
+    _check(table, "table", None, 2)
+    _check(index, "index", torch.int32, 1)
+    T, H = hidden.shape
+    if table.shape[1] != H or index.numel() != T:
+        raise KernelError(f"table {tuple(table.shape)} / index {index.numel()} do not fit hidden {(T, H)}")
+    f = _fn("elementwise", "hb_add_table_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(hidden), _p(table), _p(index), T, H, table.shape[0], _dt(table.dtype), _stream()), "add_table_rows")
+    return hidden
+
+
+def cast_rows(dst: torch.Tensor, col0: int, src: torch.Tensor) -> None:
+    """``dst[:, col0 : col0 + W] = src`` (float32 [T, W]) in dst's dtype; dst [T, ld] contiguous."""
+    _check(dst, "dst", None, 2)
+    _check(src, "src", torch.float32, 2)
+    T, W = src.shape
+    if dst.shape[0] != T or col0 < 0 or col0 + W > dst.shape[1]:
+        raise KernelError(f"columns {col0}..{col0 + W} of {tuple(dst.shape)} do not take {tuple(src.shape)}")
+    f = _fn("elementwise", "hb_cast_rows", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(dst), dst.shape[1], col0, _p(src), T, W, _dt(dst.dtype), _stream()), "cast_rows")
 
 
 # ------------------------------------------------------------------ gated activations, post-norm
@@ -1328,17 +1507,29 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, hea
 
 
 # ------------------------------------------------------------------ routed experts
-def moe_topk(logits: torch.Tensor, top: int):
-    """(expert ids int32 [T, top], weights float32 [T, top]): the ``top`` largest sigmoid
-    scores of float32 router ``logits`` [T, experts] (lower index on a tie), largest first."""
+ROUTER_KINDS = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_topk(logits: torch.Tensor, top: int, kind: str = "sigmoid",
+             correction: Optional[torch.Tensor] = None):
+    """(expert ids int32 [T, top], weights float32 [T, top]) from float32 router ``logits``
+    [T, outputs]: scores s = sigmoid(z), or softmax(z) over all outputs; the ``top`` largest
+    s + correction (float32 [outputs]; None: s alone) are chosen, lower index on a tie, largest
+    first; the weight is s itself."""
     _check(logits, "logits", torch.float32, 2)
     T, E = logits.shape
+    if kind not in ROUTER_KINDS:
+        raise KernelError(f"router kind {kind!r} is not one of {sorted(ROUTER_KINDS)}")
     if not 0 < top <= min(E, 16):
         raise KernelError(f"top {top} of {E} experts is not supported (1..16)")
+    if correction is not None:
+        _check(correction, "correction", torch.float32, 1)
+        if correction.numel() != E:
+            raise KernelError(f"correction has {correction.numel()} entries for {E} router outputs")
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    f = _fn("moe", "hb_moe_topk", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(ids), _p(weights), _p(logits), T, E, top, _stream()), "moe_topk")
+    f = _fn("moe", "hb_moe_topk", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(ids), _p(weights), _p(logits), _p(correction), T, E, top, ROUTER_KINDS[kind], _stream()), "moe_topk")
     return ids, weights
 
 
@@ -1349,39 +1540,56 @@ def moe_topk(logits: torch.Tensor, top: int):
 #: grouped path takes 0.1.  Float32, and inner sizes or widths that are no multiple of 8,
 #: stream every pair's expert rows.
 MOE_GROUPED_MIN_TOKENS = 1
+#: gates an expert may have (codes of ``GLU_KINDS``)
+MOE_GATES = ("silu", "clamped_swish")
 
 
 def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                        w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float) -> torch.Tensor:
-    """``moe_experts`` for many tokens: sort the pairs by expert, scale and scatter the rows,
+                        w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float,
+                        gate: str = "clamped_swish", weight_on: str = "input", identity: int = 0,
+                        base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``moe_experts`` for many tokens: sort the pairs by expert, (scale and) scatter the rows,
     one grouped product for gate|up, the gate, one for down, and a gather that adds a token's
-    choices in their order."""
+    choices in their order (times their weights where those belong on the output).  Pairs of
+    the experts without tensors sort behind all others: the products leave their rows alone
+    and the gather takes the token's own row for them."""
     T, width = h.shape
     E, two_ff, _ = w_gate_up.shape
     top = ids.shape[1]
     pairs = T * top
-    ends = torch.empty((E,), dtype=torch.int32, device=h.device)
+    on_output = weight_on == "output"
+    ends = torch.empty((E + identity,), dtype=torch.int32, device=h.device)
     place = torch.empty((pairs,), dtype=torch.int32, device=h.device)
     f = _fn("moe", "hb_moe_sort", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _run(f(_p(ends), _p(place), _p(ids), pairs, E, _stream()), "moe_sort")
+    _run(f(_p(ends), _p(place), _p(ids), pairs, E + identity, _stream()), "moe_sort")
     rows = torch.empty((pairs, width), dtype=h.dtype, device=h.device)
     f = _fn("moe", "hb_moe_scatter_rows",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(rows), _p(h), _p(place), _p(weights), T, top, width, _dt(h.dtype), _stream()), "moe_scatter_rows")
-    gate_up = torch._grouped_mm(rows, w_gate_up.transpose(1, 2), offs=ends)
-    y = glu_act(gate_up, "clamped_swish", limit)
-    down = torch._grouped_mm(y, w_down.transpose(1, 2), offs=ends)
+    _run(f(_p(rows), _p(h), _p(place), 0 if on_output else _p(weights), T, top, width, _dt(h.dtype),
+           _stream()), "moe_scatter_rows")
+    offs = ends[:E] if identity else ends
+    gate_up = torch._grouped_mm(rows, w_gate_up.transpose(1, 2), offs=offs)
+    y = glu_act(gate_up, gate, limit)
+    down = torch._grouped_mm(y, w_down.transpose(1, 2), offs=offs)
     out = torch.empty((T, width), dtype=h.dtype, device=h.device)
-    f = _fn("moe", "hb_moe_gather_sum", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(out), _p(down), _p(place), T, top, width, _dt(h.dtype), _stream()), "moe_gather_sum")
+    f = _fn("moe", "hb_moe_gather_sum",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(down), _p(place), _p(ids) if identity else 0, _p(weights) if on_output else 0,
+           _p(h) if identity else 0, _p(base), E, T, top, width, _dt(h.dtype), _stream()), "moe_gather_sum")
     return out
 
 
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
-                w_down: torch.Tensor, limit: float) -> torch.Tensor:
-    """sum over a token's chosen experts of expert(weight * h): ``w_gate_up`` [experts, 2 ff,
-    width] (gate rows, then up rows), ``w_down`` [experts, width, ff], the clamped gate of
-    ``glu_act``.  Returns [T, width] in h's dtype."""
+                w_down: torch.Tensor, limit: float = 0.0, gate: str = "clamped_swish",
+                weight_on: str = "input", identity: int = 0,
+                base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The sum over a token's chosen experts: of expert(weight * h) with ``weight_on`` =
+    "input", of weight * expert(h) with "output".  ``w_gate_up`` [experts, 2 ff, width] (gate
+    rows, then up rows), ``w_down`` [experts, width, ff]; ``gate``: "clamped_swish" with its
+    ``limit`` or "silu" (``glu_act``).  Expert ids from ``experts`` up to ``experts + identity``
+    name experts without tensors, whose output is their input (times the weight).  ``base``
+    ([T, width]) is added to the sum.  Returns [T, width] in h's dtype."""
     _check(h, "h", None, 2)
     _check(ids, "ids", torch.int32, 2)
     _check(weights, "weights", torch.float32, 2)
@@ -1394,16 +1602,23 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     if w2 != width or tuple(w_down.shape) != (E, width, ff) or tuple(ids.shape) != (T, top) \
             or ids.shape != weights.shape:
         raise KernelError("moe_experts: shapes do not fit")
+    if gate not in MOE_GATES or weight_on not in ("input", "output") or identity < 0:
+        raise KernelError(f"moe_experts: gate {gate!r} / weight_on {weight_on!r} / identity {identity}")
+    if base is not None:
+        _check(base, "base", h.dtype, 2)
+        if tuple(base.shape) != (T, width):
+            raise KernelError("moe_experts: base does not fit")
     if h.dtype == torch.bfloat16 and T >= MOE_GROUPED_MIN_TOKENS and width % 8 == 0 and ff % 8 == 0 \
             and hasattr(torch, "_grouped_mm"):
-        return moe_experts_grouped(h, ids, weights, w_gate_up, w_down, limit)
+        return moe_experts_grouped(h, ids, weights, w_gate_up, w_down, limit, gate, weight_on, identity, base)
     partial = torch.empty((T * top, width), dtype=torch.float32, device=h.device)
     f = _fn("moe", "hb_moe_expert_rows",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-             c_float, c_int, c_void_p])
+             c_float, c_int, c_int, c_int, c_int, c_void_p])
     _run(f(_p(partial), _p(h), _p(w_gate_up), _p(w_down), _p(ids), _p(weights), T, top, width, ff,
-           float(limit), _dt(h.dtype), _stream()), "moe_expert_rows")
+           float(limit), GLU_KINDS[gate], 1 if weight_on == "output" else 0, E, _dt(h.dtype), _stream()),
+         "moe_expert_rows")
     out = torch.empty((T, width), dtype=h.dtype, device=h.device)
-    f = _fn("moe", "hb_moe_combine", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(out), _p(partial), T, width, top, _dt(h.dtype), _stream()), "moe_combine")
+    f = _fn("moe", "hb_moe_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(partial), _p(base), T, width, top, _dt(h.dtype), _stream()), "moe_combine")
     return out

@@ -67,6 +67,8 @@ class StepContext:
     norm_after_block: object = None
     # index of the schedule entry that runs now
     run_index: int = 0
+    # the stream as the input stage left it, kept for a stage between blocks that asks for it
+    stream_input: Optional[torch.Tensor] = None
     extras: dict = field(default_factory=dict)
 
     def part_state(self, part) -> Optional[torch.Tensor]:

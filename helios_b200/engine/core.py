@@ -156,6 +156,10 @@ class EngineCore:
         self.model = model
         self.cache = KVCacheManager(model.plan, page_size, num_pages, max_slots, model.dtype,
                                     model.device, watermark=watermark, poison=poison_cache)
+        # a position encoding with a table bounds every request's length
+        table = getattr(model.plan.position, "max_positions", None)
+        if table is not None:
+            max_model_len = min(max_model_len or table, table)
         self.max_model_len = max_model_len
         self.vocab_size = model.plan.vocab_size
         self.steps_run = 0

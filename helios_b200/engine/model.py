@@ -11,6 +11,7 @@ from .. import models as _models  # registers the architectures
 from ..config.registry import resolve_architecture, typed_config
 from ..config.model_config import read_config_json
 from ..parts import ModelPlan
+from ..parts.base import settle
 from ..weights import bind_random_weights, load_weights
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -77,19 +78,27 @@ class DecoderModel:
         residual = plan.embedding.forward(ctx)
         if plan.position is not None:
             residual = plan.position.embed(ctx, residual)
+        ctx.stream_input = residual.clone() if any(s.needs_input for s in plan.stages.values()) else None
         delta = None
         runs = len(plan.schedule)
         for entry, run in enumerate(plan.schedule):
+            if run.before is not None:
+                # a stage between blocks takes the stream with nothing pending
+                settle(residual, delta)
+                residual, delta = plan.stages[run.before].forward(ctx, residual), None
             ctx.block_states = cache.part_states(entry)
             ctx.run_index = entry
             # the norm that meets the residual stream first after this block, if the next
-            # block says so: a part may prepare it while it adds its own output
+            # block says so (and no stage stands between): a part may prepare it while it adds
+            # its own output
             ctx.norm_after_block = (plan.layers[plan.schedule[entry + 1].layer].first_norm
-                                    if entry + 1 < runs else None)
+                                    if entry + 1 < runs and plan.schedule[entry + 1].before is None
+                                    else None)
             residual, delta = plan.layers[run.layer].forward(
                 ctx, residual, delta, cache.layer_cache(entry), cache.layer_state(entry))
         ctx.block_states = {}
         ctx.norm_after_block = None
+        ctx.stream_input = None
         if ctx.num_wanted == 0:
             return None
         return plan.output.forward(ctx, residual, delta)

@@ -1,6 +1,8 @@
 """Plan builders; importing this package registers the architectures."""
-from . import dense_decoder, zokelix
+from . import dense_decoder, mizerax, zokelix
 from .dense_decoder import build_dense_decoder_plan
+from .mizerax import build_mizerax_plan
 from .zokelix import build_zokelix_plan
 
-__all__ = ["build_dense_decoder_plan", "build_zokelix_plan", "dense_decoder", "zokelix"]
+__all__ = ["build_dense_decoder_plan", "build_mizerax_plan", "build_zokelix_plan", "dense_decoder", "mizerax",
+           "zokelix"]

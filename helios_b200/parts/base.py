@@ -44,6 +44,7 @@ class PagedCacheSpec:
     head_dim: int
     window: Optional[int] = None      # None: every key is needed; W: only the last W
     planes: int = 2                   # 2: keys and values; 1: one row a token (a latent cache)
+    value_dim: Optional[int] = None   # values per head where they differ from head_dim (planes 2)
 
 
 @dataclass(frozen=True)
@@ -90,6 +91,9 @@ class Norm(Part):
                     out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``residual += delta`` in float32 (in place, unless ``rows`` selects) and the
         normed rows in ``out_dtype``.  The default does it in two steps."""
+        if isinstance(delta, PendingSum):
+            settle(residual, delta)          # the default knows no better than to add first
+            delta = None
         if rows is not None:
             r = residual.index_select(0, rows.long())
             if delta is not None:
@@ -109,6 +113,10 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    #: positions the encoding has (a learned table); None: any.  The step function refuses a
+    #: request that would grow beyond it.
+    max_positions: Optional[int] = None
+
     def prepare(self, ctx) -> None:
         """Called once per step before the layers for the plan's own encoding; may leave
         tables on ``ctx`` for the mixers that were given no encoding of their own."""
@@ -147,6 +155,44 @@ class OutputStage(Part):
         return []
 
     def forward(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        raise NotImplementedError
+
+
+@dataclass
+class PendingSum:
+    """Outputs of a block that are still to be added to the residual stream:
+    ``residual += mult * sum_i scale_i * tensor_i`` (float32; a scale is a float32 vector
+    over the width, or None for 1).  A block whose sublayers all read one norm of the stream
+    returns it in the place of ``delta``; a norm that knows how (``Norm.add_forward``) does
+    the add in its own kernel, anyone else calls ``settle`` first.  At most two terms."""
+    terms: List[Tuple[torch.Tensor, Optional[torch.Tensor]]]
+    mult: float = 1.0
+
+
+def settle(residual: torch.Tensor, delta) -> None:
+    """Add whatever is pending to the float32 residual stream, in place."""
+    if delta is None:
+        return
+    if isinstance(delta, PendingSum):
+        from ..csrc import ops
+        (a, sa), (b, sb) = (delta.terms + [(None, None)])[:2]
+        ops.add_layernorm(residual, None, None, 0.0, None, a=a, scale_a=sa, b=b, scale_b=sb, mult=delta.mult)
+        return
+    if isinstance(delta, DeferredNorm):
+        raise ValueError("a deferred norm carries no pending add")
+    residual.add_(delta.float())
+
+
+class StreamStage(Part):
+    """A part that stands BETWEEN blocks and rewrites the whole residual stream: the plan
+    names the schedule entries it runs before.  ``forward`` gets the float32 stream with
+    nothing pending and returns the new stream; ``ctx.stream_input`` holds the stream as the
+    input stage left it when ``needs_input`` is set."""
+
+    #: True: the model keeps a copy of the input stage's output for this part
+    needs_input = False
+
+    def forward(self, ctx, residual: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 

@@ -10,7 +10,8 @@ from typing import List, Optional, Tuple
 
 import torch
 
-from .base import Block, DeferredNorm, FeedForward, LayerCache, Mixer, Norm, Part, register_part
+from .base import (Block, DeferredNorm, FeedForward, LayerCache, Mixer, Norm, Part, PendingSum, WeightSpec,
+                   register_part)
 
 
 class PreNormBlock(Block):
@@ -123,3 +124,71 @@ class PostNormBlock(Block):
 
 
 register_part("block", "post_norm", PostNormBlock)
+
+
+class ChannelScale(Part):
+    """A learned factor per channel on a sublayer's output (float32 in both modes)."""
+
+    def __init__(self, width: int, tensor_name: str = "") -> None:
+        self.width, self.tensor_name = width, tensor_name
+        self.scale: Optional[torch.Tensor] = None
+
+    def weight_specs(self):
+        return {self.tensor_name: WeightSpec((self.width,), kind="vector", init="ones_jitter")}
+
+    def bind(self, tensors) -> None:
+        self.scale = tensors[self.tensor_name].contiguous()
+
+
+class ParallelBlock(Block):
+    """x + mult * (ls1 * mixer(h) + ls2 * feed_forward(h)) with h = norm(x): ONE norm, and both
+    sublayers read its output.  ``ls1`` / ``ls2`` are learned per-channel factors
+    (``layer_scale``; without it they are 1); the feed-forward may be absent.  The sum is not
+    formed here: the block returns its outputs as a ``PendingSum``, and the norm that meets the
+    stream next adds them in float32 in its own kernel."""
+
+    def __init__(self, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward] = None, mult: float = 1.0,
+                 layer_scale: bool = True, names: Tuple[str, str, str, str, str] =
+                 ("norm1", "mix.", "mlp.", "ls1", "ls2")) -> None:
+        self.norm = norm
+        self._mixer = mixer
+        self.ffn = ffn
+        self.mult = float(mult)
+        self.names = names
+        width = getattr(norm, "width")
+        self.mixer_scale = ChannelScale(width) if layer_scale else None
+        self.ffn_scale = ChannelScale(width) if layer_scale and ffn is not None else None
+
+    @property
+    def mixer(self) -> Mixer:
+        return self._mixer
+
+    def named_parts(self) -> List[Tuple[str, Part]]:
+        n_norm, n_mix, n_ffn, n_ls1, n_ls2 = self.names
+        parts = [(n_norm, self.norm), (n_mix, self._mixer)]
+        if self.ffn is not None:
+            parts.append((n_ffn, self.ffn))
+        if self.mixer_scale is not None:
+            parts.append((n_ls1, self.mixer_scale))
+        if self.ffn_scale is not None:
+            parts.append((n_ls2, self.ffn_scale))
+        return parts
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for _, p in self.named_parts())
+
+    def forward(self, ctx, residual: torch.Tensor, delta, cache: Optional[LayerCache],
+                state: Optional[torch.Tensor]):
+        if isinstance(delta, DeferredNorm):
+            raise ValueError("a parallel block takes no deferred norm")
+        h = self.norm.add_forward(residual, delta, ctx.act_dtype)
+        terms = [(self._mixer.forward(ctx, h, cache, state),
+                  self.mixer_scale.scale if self.mixer_scale is not None else None)]
+        if self.ffn is not None:
+            terms.append((self.ffn.forward(ctx, h),
+                          self.ffn_scale.scale if self.ffn_scale is not None else None))
+        return residual, PendingSum(terms, self.mult)
+
+
+register_part("block", "parallel", ParallelBlock)

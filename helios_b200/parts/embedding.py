@@ -6,7 +6,7 @@ from typing import Dict
 import torch
 
 from ..csrc import ops
-from .base import InputStage, Norm, OutputStage, Part, WeightSpec
+from .base import InputStage, Norm, OutputStage, Part, PositionEncoding, WeightSpec, register_part
 
 
 class TokenEmbedding(InputStage):
@@ -74,3 +74,28 @@ class NormedHead(OutputStage):
     def forward(self, ctx, residual: torch.Tensor, delta) -> torch.Tensor:
         rows = self.norm.add_forward(residual, delta, ctx.act_dtype, rows=ctx.want_rows)
         return self.head.forward(ctx, rows)
+
+
+class LearnedPositions(PositionEncoding):
+    """A learned vector per position, added (unscaled, in float32) to the embedded tokens:
+    hidden[t] += table[position of t].  Positions count from 0 in every request and stay
+    below ``max_positions``: the step function refuses a request that would pass it."""
+
+    def __init__(self, max_positions: int, width: int, tensor_name: str = "weight") -> None:
+        self.max_positions = max_positions
+        self.width = width
+        self.tensor_name = tensor_name
+        self.table = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.tensor_name: WeightSpec((self.max_positions, self.width))}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.table = tensors[self.tensor_name].contiguous()
+
+    def embed(self, ctx, hidden: torch.Tensor) -> torch.Tensor:
+        # the engine keeps every request below ``max_positions`` (``PositionEncoding.max_positions``)
+        return ops.add_table_rows(hidden, self.table, ctx.positions)
+
+
+register_part("position_encoding", "learned", LearnedPositions)

@@ -9,10 +9,21 @@ The weight is the expert's score itself, not renormalised over the chosen ones, 
 multiplies the expert's INPUT (the experts are not linear, so this is not the same as
 weighting their outputs).  An expert is down(act(gate x) * up x) without biases, with the
 activation and its constants as parameters (the clamped form of ``ops.glu_act`` here).
+
+Options, each a constructor parameter with the form above as its default:
+
+``router``      "sigmoid", or "softmax" over ALL router outputs
+``correction``  a vector from the checkpoint that is added to the scores for the CHOICE only
+                (the weights stay the scores)
+``weight_on``   "input", or "output": out = sum of s_e * expert_e(h)
+``activation``  "clamped_swish" (with ``limit``) or "silu"
+``identity``    this many router outputs beyond the experts stand for experts without
+                tensors whose output is their input
+``shared_inner`` an expert of this inner size (same form) that every token runs, added to the sum
 """
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
@@ -21,15 +32,28 @@ from .base import FeedForward, WeightSpec, register_part
 
 
 class RoutedExperts(FeedForward):
-    def __init__(self, width: int, inner: int, experts: int, top: int, limit: float,
+    def __init__(self, width: int, inner: int, experts: int, top: int, limit: float = 0.0,
                  router_name: str = "router", expert_prefix: str = "e",
-                 names=("gate", "up", "down")) -> None:
-        if not 0 < top <= experts:
-            raise ValueError(f"top {top} of {experts} experts")
+                 names=("gate", "up", "down"), router: str = "sigmoid", correction: bool = False,
+                 weight_on: str = "input", activation: str = "clamped_swish", identity: int = 0,
+                 shared_inner: Optional[int] = None, correction_name: str = "correction",
+                 shared_prefix: str = "shared.") -> None:
+        if not 0 < top <= experts + identity:
+            raise ValueError(f"top {top} of {experts} + {identity} experts")
+        if router not in ops.ROUTER_KINDS or weight_on not in ("input", "output") \
+                or activation not in ops.MOE_GATES:
+            raise ValueError(f"router {router!r} / weight_on {weight_on!r} / activation {activation!r}")
+        if identity and weight_on != "output":
+            raise ValueError("experts without tensors need the weight on the output")
         self.width, self.inner, self.experts, self.top = width, inner, experts, top
         self.limit = float(limit)
         self.router_name, self.expert_prefix, self.names = router_name, expert_prefix, tuple(names)
+        self.router, self.weight_on, self.activation = router, weight_on, activation
+        self.identity, self.shared_inner = int(identity), shared_inner
+        self.has_correction, self.correction_name = bool(correction), correction_name
+        self.shared_prefix = shared_prefix
         self.w_router = self.w_gate_up = self.w_down = None
+        self.correction = self.w_shared_gate_up = self.w_shared_down = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         g, u, d = self.names
@@ -39,7 +63,15 @@ class RoutedExperts(FeedForward):
             specs[p + g] = WeightSpec((self.inner, self.width))
             specs[p + u] = WeightSpec((self.inner, self.width))
             specs[p + d] = WeightSpec((self.width, self.inner))
-        specs[self.router_name] = WeightSpec((self.experts, self.width))
+        outputs = self.experts + self.identity
+        specs[self.router_name] = WeightSpec((outputs, self.width))
+        if self.has_correction:
+            specs[self.correction_name] = WeightSpec((outputs,), kind="vector", init="normal")
+        if self.shared_inner:
+            p = self.shared_prefix
+            specs[p + g] = WeightSpec((self.shared_inner, self.width))
+            specs[p + u] = WeightSpec((self.shared_inner, self.width))
+            specs[p + d] = WeightSpec((self.width, self.shared_inner))
         return specs
 
     def kernel_libraries(self, dtype):
@@ -52,11 +84,26 @@ class RoutedExperts(FeedForward):
         self.w_gate_up = torch.stack([torch.cat([tensors[f"{p}{e}.{g}"], tensors[f"{p}{e}.{u}"]], dim=0)
                                       for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[f"{p}{e}.{d}"] for e in range(self.experts)]).contiguous()
+        if self.has_correction:
+            self.correction = tensors[self.correction_name].contiguous()
+        if self.shared_inner:
+            p = self.shared_prefix
+            self.w_shared_gate_up = torch.cat([tensors[p + g], tensors[p + u]], dim=0).contiguous()
+            self.w_shared_down = tensors[p + d].contiguous()
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        logits = ops.linear_logits(x, self.w_router)          # float32 [T, experts]
-        ids, weights = ops.moe_topk(logits, self.top)
-        return ops.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, self.limit)
+        logits = ops.linear_logits(x, self.w_router)          # float32 [T, router outputs]
+        ids, weights = ops.moe_topk(logits, self.top, self.router, self.correction)
+        base = None
+        if self.shared_inner:
+            if self.activation == "silu":
+                inner = ops.linear_swiglu(x, self.w_shared_gate_up)
+            else:
+                inner = ops.glu_act(ops.linear(x, self.w_shared_gate_up), self.activation, self.limit)
+            base = ops.linear(inner, self.w_shared_down)
+        return ops.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, self.limit,
+                               gate=self.activation, weight_on=self.weight_on, identity=self.identity,
+                               base=base)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

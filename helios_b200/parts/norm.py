@@ -7,7 +7,7 @@ from typing import Dict, Optional
 import torch
 
 from ..csrc import ops
-from .base import Norm, WeightSpec, register_part
+from .base import Norm, PendingSum, WeightSpec, register_part, settle
 
 
 class RMSNorm(Norm):
@@ -29,6 +29,9 @@ class RMSNorm(Norm):
         return ops.rmsnorm(x, self.weight, self.eps)
 
     def add_forward(self, residual, delta, out_dtype, rows=None):
+        if isinstance(delta, PendingSum):
+            settle(residual, delta)
+            delta = None
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out_dtype, rows)
 
     def add_normed(self, residual, y, out_dtype):
@@ -37,3 +40,45 @@ class RMSNorm(Norm):
 
 
 register_part("norm", "rmsnorm", RMSNorm)
+
+
+class LayerNorm(Norm):
+    """(x - mean) / sqrt(mean((x - mean)^2) + eps) * weight + bias, statistics in float32; weight
+    and bias stay float32 in both modes.  ``weight_name`` / ``bias_name``: the tensors' names
+    below the part's prefix (the weight's may be "", where the checkpoint names the norm
+    itself); ``bias=False``: no bias tensor.
+
+    ``add_forward`` takes a ``PendingSum`` in the place of ``delta`` and does that add, scales
+    and multiplier included, in the norm's own kernel."""
+
+    def __init__(self, width: int, eps: float, weight_name: str = "weight", bias_name: str = "bias",
+                 bias: bool = True) -> None:
+        self.width = width
+        self.eps = float(eps)
+        self.weight_name, self.bias_name, self.has_bias = weight_name, bias_name, bool(bias)
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = {self.weight_name: WeightSpec((self.width,), kind="vector", init="ones_jitter")}
+        if self.has_bias:
+            specs[self.bias_name] = WeightSpec((self.width,), kind="vector", init="normal")
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].contiguous()
+        self.bias = tensors[self.bias_name].contiguous() if self.has_bias else None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """The norm of rows in the activation dtype (statistics still float32)."""
+        return ops.add_layernorm(x.float().contiguous(), self.weight, self.bias, self.eps, x.dtype)
+
+    def add_forward(self, residual, delta, out_dtype, rows=None):
+        if isinstance(delta, PendingSum):
+            (a, sa), (b, sb) = (delta.terms + [(None, None)])[:2]
+            return ops.add_layernorm(residual, self.weight, self.bias, self.eps, out_dtype, rows,
+                                     a=a, scale_a=sa, b=b, scale_b=sb, mult=delta.mult)
+        return ops.add_layernorm(residual, self.weight, self.bias, self.eps, out_dtype, rows, a=delta)
+
+
+register_part("norm", "layernorm", LayerNorm)

@@ -12,7 +12,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Dict, Iterator, List, Optional, Tuple
 
-from .base import Block, InputStage, Norm, OutputStage, Part, PositionEncoding
+from .base import Block, InputStage, Norm, OutputStage, Part, PositionEncoding, StreamStage
 from .embedding import NormedHead
 
 
@@ -21,6 +21,7 @@ class Run:
     layer: int
     cache: Optional[int] = None        # None: this entry's own index in the schedule
     writes_cache: bool = True
+    before: Optional[str] = None       # a stage of ``ModelPlan.stages`` that rewrites the stream first
 
 
 @dataclass
@@ -45,6 +46,8 @@ class ModelPlan:
     tied: Dict[str, str] = field(default_factory=dict)
     # suffixes of checkpoint tensors that are buffers, not weights
     benign_suffixes: Tuple[str, ...] = (".rotary_emb.inv_freq", ".attn.bias", ".attn.masked_bias")
+    # checkpoint prefix -> a part that rewrites the stream between blocks (``Run.before``)
+    stages: Dict[str, StreamStage] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
         if self.output is None:
@@ -57,6 +60,8 @@ class ModelPlan:
         for i, run in enumerate(self.schedule):
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"schedule entry {i} names layer {run.layer} of {len(self.layers)}")
+            if run.before is not None and run.before not in self.stages:
+                raise ValueError(f"schedule entry {i} names the stage {run.before!r}, which the plan lacks")
             cid = self.cache_id(i)
             if cid != i:
                 if not 0 <= cid < i:
@@ -76,6 +81,7 @@ class ModelPlan:
         for prefix, block in zip(self.layer_prefixes, self.layers):
             for sub, part in block.named_parts():
                 yield prefix + sub, part
+        yield from self.stages.items()
         yield from self.output.named_parts()
 
     @property
