@@ -23,6 +23,7 @@
 #include <type_traits>
 #include "common.cuh"
 #include "attention_mma.cuh"
+#include "attention_options.cuh"
 
 namespace {
 
@@ -100,7 +101,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const int* __restrict__ positions, int nh, int nkv, int page_size,
                         int window, float scale_log2, int n_splits, int cluster_merge,
                         const float* __restrict__ rot_cos, const float* __restrict__ rot_sin,
-                        __nv_bfloat16* k_write, __nv_bfloat16* v_write) {
+                        __nv_bfloat16* k_write, __nv_bfloat16* v_write, AttnOptions opt) {
   // rot_cos / rot_sin [requests, HD / 2]: q (and the new key) still lack their rotation.
   // k_write / v_write (the cache again, writable): the new token's key and value are still
   // in the q|k|v row and go into the cache here.
@@ -127,6 +128,13 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   const int tile_begin = split * tiles_per_split;
   const int tile_end = min(tiles_total, tile_begin + tiles_per_split);
   const int k_end = pos + 1;
+  // slopes of the distance bias for this thread's two rows of the tile (heads g0 and g0 + 8)
+  float slope_log2[2] = {0.f, 0.f};
+  if (opt.slopes != nullptr) {
+    const int g0 = lane >> 2;
+    if (g0 < G) slope_log2[0] = opt.slopes[kvh * G + g0] * LOG2E;
+    if (g0 + 8 < G) slope_log2[1] = opt.slopes[kvh * G + g0 + 8] * LOG2E;
+  }
   const int* table = block_table + (size_t)seq * bt_stride;
 
   __nv_bfloat16* my = smem + (size_t)warp * DEC_STAGES * 2 * TILE_ELEMS;   // [stage][k|v][tile]
@@ -284,7 +292,19 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
       for (int i = 0; i < DEC_TILE / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
       qk_tile<HD, DEC_TILE / 8>(s, qa, kt, lane);
       const int tile_key0 = first + tile * DEC_TILE;
-      if (tile_key0 + DEC_TILE > k_end || tile_key0 < lo) {
+      if (opt.slopes != nullptr) {
+        // a bias that grows with the distance, for every row (head) of the tile; and the masks
+        const int key0 = tile_key0 + 2 * (lane & 3);
+#pragma unroll
+        for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = key0 + nt * 8 + (e & 1);
+            s[nt][e] = (key < k_end && key >= lo)
+                ? fmaf(s[nt][e], scale_log2, -slope_log2[e >> 1] * (float)(pos - key)) : -INFINITY;
+          }
+        }
+      } else if (tile_key0 + DEC_TILE > k_end || tile_key0 < lo) {
         // the last tile (keys beyond the token's own) or the first (keys before the window)
         const int key0 = tile_key0 + 2 * (lane & 3);
 #pragma unroll
@@ -356,7 +376,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
     const int h = kvh * G + row;
     if (n_splits == 1) {
-      out[((size_t)seq * nh + h) * HD + d] = __float2bfloat16_rn(acc / L);
+      out[((size_t)seq * nh + h) * HD + d] =
+          __float2bfloat16_rn(attn_finish(acc, M, L, opt.sink, attn_gate_factor(opt, seq, h)));
     } else if (cluster_merge) {
       // the slices of this (request, KV head) are one thread-block cluster: park the block's
       // partial result in its own shared memory for the merge below
@@ -410,7 +431,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         L += ls[sp] * f;
         acc += os[sp] * f;
       }
-      out[((size_t)seq * nh + kvh * G + row) * HD + d] = __float2bfloat16_rn(acc / L);
+      out[((size_t)seq * nh + kvh * G + row) * HD + d] =
+          __float2bfloat16_rn(attn_finish(acc, M, L, opt.sink, attn_gate_factor(opt, seq, kvh * G + row)));
     }
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
@@ -418,10 +440,12 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 
 template <int HD>
 __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
-                                    const float* __restrict__ part_ml, int n_splits) {
+                                    const float* __restrict__ part_ml, int n_splits, int nh,
+                                    AttnOptions opt) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;   // seq * nh + head
+  const float gate_factor = attn_gate_factor(opt, row / nh, (int)(row % nh));
   const float* ml = part_ml + row * n_splits * 2;
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
@@ -431,7 +455,7 @@ __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, const float
     float acc = 0.f;
     for (int s = 0; s < n_splits; ++s)
       acc += part_o[(row * n_splits + s) * HD + d] * exp2f(ml[2 * s] - M);
-    out[row * HD + d] = __float2bfloat16_rn(acc / L);
+    out[row * HD + d] = __float2bfloat16_rn(attn_finish(acc, M, L, opt.sink, gate_factor));
   }
 }
 
@@ -447,7 +471,8 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
                          const int* __restrict__ block_table, int bt_stride,
                          const int* __restrict__ q_tiles, const int* __restrict__ cu_tokens,
                          const int* __restrict__ start_pos, int nh, int nkv, int heads_per_block,
-                         int token_subtiles, int page_size, int window, float scale_log2) {
+                         int token_subtiles, int page_size, int window, float scale_log2,
+                         AttnOptions opt) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int RS = HD + 8;
@@ -474,6 +499,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int g_in_kv = hb * heads_per_block + head_local;
   const bool active = sub < token_subtiles && g_in_kv < G && (t0 + sub * 16) < n_tok;
   const int h = kvh * G + g_in_kv;
+  const float head_slope_log2 = (opt.slopes != nullptr && g_in_kv < G) ? opt.slopes[h] * LOG2E : 0.f;
   const int g0 = lane >> 2, c0 = 2 * (lane & 3);
   // the two rows of this thread: local tokens and their positions
   const int tl0 = t0 + sub * 16 + g0, tl1 = tl0 + 8;
@@ -543,7 +569,10 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
           const int key = key_base + nt * 8 + c0 + (e & 1);
           const int pr = (e >> 1) ? pr1 : pr0;
           const bool ok = key <= pr && (window <= 0 || key > pr - window);
-          s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
+          if (opt.slopes != nullptr)
+            s[nt][e] = ok ? fmaf(s[nt][e], scale_log2, -head_slope_log2 * (float)(pr - key)) : -INFINITY;
+          else
+            s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
         }
       }
       softmax_step<HD, PRE_TILE / 8>(s, m, l, o);
@@ -562,7 +591,8 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   for (int r = 0; r < 2; ++r) {
     const int tl = r ? tl1 : tl0;
     if (tl >= n_tok) continue;
-    const float inv = 1.f / l[r];
+    // attn_finish(1, m, l, ...) is the factor on every value of the row (1 / l without options)
+    const float inv = attn_finish(1.f, m[r], l[r], opt.sink, attn_gate_factor(opt, tok0 + tl, h));
     __nv_bfloat16* orow = out + ((size_t)(tok0 + tl) * nh + h) * HD;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
@@ -577,7 +607,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
                   const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                   const int* positions, int S, int nh, int nkv, int page_size, int window,
                   float scale, int n_splits, const float* rot_cos, const float* rot_sin,
-                  int write_cache, cudaStream_t stream) {
+                  int write_cache, AttnOptions opt, cudaStream_t stream) {
   constexpr int RS = HD + 8;
   // the new keys and values go into the very pages the kernel reads
   __nv_bfloat16* k_write = write_cache ? (__nv_bfloat16*)const_cast<void*>(k_pages) : nullptr;
@@ -613,17 +643,17 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
     cudaLaunchKernelEx(&cfg, kernel, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
                        positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 1,
-                       rot_cos, rot_sin, k_write, v_write);
+                       rot_cos, rot_sin, k_write, v_write, opt);
     return hb_check_launch();
   }
   hb_launch(kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 
       (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
       positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 0,
-      rot_cos, rot_sin, k_write, v_write);
+      rot_cos, rot_sin, k_write, v_write, opt);
   if (n_splits > 1)
     hb_launch(decode_merge_kernel<HD>, dim3(S * nh), dim3(HD < 128 ? HD : 128), 0, stream, 
-        (__nv_bfloat16*)out, part_o, part_ml, n_splits);
+        (__nv_bfloat16*)out, part_o, part_ml, n_splits, nh, opt);
   return hb_check_launch();
 }
 
@@ -659,7 +689,8 @@ template <int HD>
 int launch_prefill(void* out, const void* q, int q_stride, const void* k_pages, const void* v_pages,
                    const int* block_table, int bt_stride, const int* q_tiles, int n_tiles,
                    const int* cu_tokens, const int* start_pos, int nh, int nkv, int heads_per_block,
-                   int token_subtiles, int page_size, int window, float scale, cudaStream_t stream) {
+                   int token_subtiles, int page_size, int window, float scale, AttnOptions opt,
+                   cudaStream_t stream) {
   constexpr int RS = HD + 8;
   const size_t smem = (size_t)4 * PRE_TILE * RS * sizeof(__nv_bfloat16);
   auto kernel = prefill_attention_kernel<HD>;
@@ -675,7 +706,7 @@ int launch_prefill(void* out, const void* q, int q_stride, const void* k_pages, 
   hb_launch(kernel, dim3(grid), dim3(PRE_WARPS * 32), smem, stream, 
       (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, block_table, bt_stride, q_tiles, cu_tokens, start_pos, nh, nkv,
-      heads_per_block, token_subtiles, page_size, window, scale * LOG2E);
+      heads_per_block, token_subtiles, page_size, window, scale * LOG2E, opt);
   return hb_check_launch();
 }
 
@@ -706,8 +737,10 @@ HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml,
                                        int S, int nh, int nkv, int hd, int page_size, int window,
                                        float scale, int n_splits, const float* rot_cos,
                                        const float* rot_sin, int write_cache, int warps,
-                                       cudaStream_t stream) {
+                                       const float* slopes, int sink, const void* gate,
+                                       int gate_stride, cudaStream_t stream) {
   if (S <= 0) return HB_OK;
+  const AttnOptions opt = {slopes, (const __nv_bfloat16*)gate, gate_stride, sink};
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || page_size <= 0 || n_splits < 1 ||
       (warps != 4 && warps != 8))
     return HB_BAD_ARGUMENT;
@@ -718,7 +751,7 @@ HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml,
   HB_DISPATCH_HD(hd, return (launch_decode<HD, W>(out, part_o, part_ml, q, q_stride, k_pages, v_pages, \
                                                   block_table, bt_stride, positions, S, nh, nkv,      \
                                                   page_size, window, scale, n_splits, rot_cos,        \
-                                                  rot_sin, write_cache, stream)))
+                                                  rot_sin, write_cache, opt, stream)))
   if (warps == 8) HB_DECODE(8);
   HB_DECODE(4);
 #undef HB_DECODE
@@ -737,13 +770,15 @@ HB_EXPORT int hb_attention_prefill_bf16(void* out, const void* q, int q_stride, 
                                         const int* q_tiles, int n_tiles, const int* cu_tokens,
                                         const int* start_pos, int nh, int nkv, int hd,
                                         int heads_per_block, int token_subtiles, int page_size,
-                                        int window, float scale, cudaStream_t stream) {
+                                        int window, float scale, const float* slopes, int sink,
+                                        const void* gate, int gate_stride, cudaStream_t stream) {
   if (n_tiles <= 0) return HB_OK;
+  const AttnOptions opt = {slopes, (const __nv_bfloat16*)gate, gate_stride, sink};
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || heads_per_block < 1 || token_subtiles < 1 ||
       heads_per_block * token_subtiles > PRE_WARPS)
     return HB_BAD_ARGUMENT;
   HB_DISPATCH_HD(hd, return launch_prefill<HD>(out, q, q_stride, k_pages, v_pages, block_table,
                                                bt_stride, q_tiles, n_tiles, cu_tokens, start_pos,
                                                nh, nkv, heads_per_block, token_subtiles, page_size,
-                                               window, scale, stream));
+                                               window, scale, opt, stream));
 }

@@ -23,6 +23,7 @@
 // Every mbarrier wait is bounded; on a timeout the block raises the error word, frees its
 // tensor memory and returns.
 #include "tcgen05.cuh"
+#include "attention_options.cuh"
 
 namespace {
 
@@ -32,6 +33,7 @@ constexpr int TC_THREADS = 352;      // warp 0: TMA of K, warp 1: MMA, warps 2-9
 constexpr int SOFTMAX_THREADS = 256;
 
 struct AttnArgs {
+  AttnOptions opt;          // distance bias, sink, gate (all off when zeroed)
   __nv_bfloat16* out;
   const __nv_bfloat16* q;
   int q_stride;
@@ -232,6 +234,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const bool row_valid = m < TQ * G && tl < n_tok;       // rows beyond TQ * G idle when G does not divide 128
     const int pr = sp + tl;                        // the row's position
     const int tid = threadIdx.x - 64;
+    // with a distance bias the scores are scaled and biased as they come out of tensor
+    // memory, and the factor on them further down is 1
+    const bool biased = a.opt.slopes != nullptr;
+    const float slope_log2 = (biased && row_valid) ? a.opt.slopes[kvh * G + g] * LOG2E : 0.f;
+    const float sc = biased ? 1.f : a.scale_log2;
 
     // stage Q: rows = (token, head) pairs, swizzled K-major; invalid rows are zero.  All
     // loads of a thread are issued before the first store (one round trip, not one each).
@@ -287,6 +294,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(8));        // the score tile may be overwritten
+      if (biased) {
+        const float at0 = slope_log2 * (float)(key_base + half * 64 - pr);      // the bias at this thread's first key
+#pragma unroll
+        for (int j = 0; j < 64; ++j) sv[j] = fmaf(sv[j], a.scale_log2, fmaf(slope_log2, (float)j, at0));
+      }
       if (masked_tile) {
         // columns of this thread's 64 keys the row may see: [lo, hi]
         const int col0 = key_base + half * 64;
@@ -302,7 +314,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       max_exchange[((it & 1) * 2 + half) * TILE + m] = mx;
       named_barrier(2 + quarter, 64);
-      mx = fmaxf(mx, max_exchange[((it & 1) * 2 + (half ^ 1)) * TILE + m]) * a.scale_log2;
+      mx = fmaxf(mx, max_exchange[((it & 1) * 2 + (half ^ 1)) * TILE + m]) * sc;
       // move the reference?  Both threads of a row see the same numbers; the rows of a warp
       // decide together, because tensor memory is read and written by whole warps.
       const bool move = mx > m_ref + LAG || (m_ref == -INFINITY && mx > -INFINITY);
@@ -320,8 +332,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       uint32_t packed[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        const float p0 = fast_exp2(fmaf(sv[2 * j], a.scale_log2, -m_use));
-        const float p1 = fast_exp2(fmaf(sv[2 * j + 1], a.scale_log2, -m_use));
+        const float p0 = fast_exp2(fmaf(sv[2 * j], sc, -m_use));
+        const float p1 = fast_exp2(fmaf(sv[2 * j + 1], sc, -m_use));
         sum4[j & 3] += p0 + p1;
         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
         packed[j] = *reinterpret_cast<uint32_t*>(&pk);
@@ -400,7 +412,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     named_barrier(1, SOFTMAX_THREADS);
     if (half == 1) l_run += l_exchange[m];
     if (ok && row_valid && !*abort_flag) {
-      const float inv = 1.f / l_run;
+      // the factor on every value of the row: 1 / l_run without a sink or a gate
+      const float inv = attn_finish(1.f, m_ref, l_run, a.opt.sink, attn_gate_factor(a.opt, tok0 + tl, kvh * G + g));
       __nv_bfloat16* dst = a.out + ((size_t)(tok0 + tl) * a.nh + (kvh * G + g)) * HD + half * OWN;
 #pragma unroll
       for (int j = 0; j < OWN; j += 8) {
@@ -455,7 +468,8 @@ HB_EXPORT int hb_attention_prefill_tc(void* out, const void* q, int q_stride, co
                                       const void* v_pages, long long num_pages, const int* block_table,
                                       int bt_stride, const int* q_tiles, int n_tiles, const int* cu_tokens,
                                       const int* start_pos, int nh, int nkv, int hd, int page_size, int window,
-                                      float scale, int* error, cudaStream_t stream) {
+                                      float scale, int* error, const float* slopes, int sink,
+                                      const void* gate, int gate_stride, cudaStream_t stream) {
   if (n_tiles <= 0) return HB_OK;
   if (nkv <= 0 || nh % nkv != 0 || error == nullptr) return HB_BAD_ARGUMENT;
   const int G = nh / nkv;
@@ -468,6 +482,7 @@ HB_EXPORT int hb_attention_prefill_tc(void* out, const void* q, int q_stride, co
   a.block_table = block_table; a.bt_stride = bt_stride; a.q_tiles = q_tiles; a.cu_tokens = cu_tokens;
   a.start_pos = start_pos; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
   a.scale_log2 = scale * LOG2E; a.error = error;
+  a.opt.slopes = slopes; a.opt.sink = sink; a.opt.gate = (const __nv_bfloat16*)gate; a.opt.gate_stride = gate_stride;
   const long long rows = num_pages * nkv * page_size;
   if (hd == 128) return launch_tc<128>(a, k_pages, v_pages, rows, n_tiles, stream);
   if (hd == 64) return launch_tc<64>(a, k_pages, v_pages, rows, n_tiles, stream);

@@ -115,7 +115,13 @@ def attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, h
 def option_attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int,
                                value_dim: int):
     """Libraries attention with ``AttentionOptions`` may choose from at these sizes."""
-    return ("attention_generic",)
+    if dtype != torch.bfloat16 or head_dim not in TILED_HEAD_DIMS or value_dim != head_dim \
+            or not ATTENTION_OPTIONS_TILED:
+        return ("attention_generic",)
+    names = ["attention_bf16"]
+    if ATTENTION_TCGEN05 and tc_attention_supported(num_heads, num_kv_heads, head_dim, 16):
+        names.append("attention_tc")
+    return tuple(names)
 
 
 # ------------------------------------------------------------------ embedding
@@ -264,6 +270,17 @@ class AttentionOptions:
 
 
 _NO_OPTIONS = AttentionOptions()
+
+
+def _tiled_options(options: Optional[AttentionOptions], tokens: int, num_heads: int,
+                   like: torch.Tensor) -> AttentionOptions:
+    """Checked options for the tensor-core kernels, whose values have the keys' size."""
+    if options is None:
+        return _NO_OPTIONS
+    if options.value_dim is not None:
+        raise KernelError("the tensor-core attention kernels take values of the keys' size only")
+    options.check(tokens, num_heads, like)
+    return options
 
 
 def attention_generic(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -767,6 +784,8 @@ def linear_logits(rows: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 
 TILED_HEAD_DIMS = (32, 64, 96, 128)
+#: attention with options (bias, sink, gate) on the tensor-core kernels where the sizes allow
+ATTENTION_OPTIONS_TILED = True
 #: merge the context slices of decode attention inside a thread-block cluster (up to 8 slices)
 ATTENTION_CLUSTER_MERGE = True
 #: steps of single tokens: rotary position encoding and cache write inside the decode kernel
@@ -874,9 +893,11 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
                           block_table: torch.Tensor, positions: torch.Tensor, num_heads: int,
                           num_kv_heads: int, head_dim: int, page_size: int,
                           window: Optional[int], scale: float, n_splits: int,
-                          rotary=None, write_cache: bool = False, warps: Optional[int] = None) -> torch.Tensor:
+                          rotary=None, write_cache: bool = False, warps: Optional[int] = None,
+                          options: Optional[AttentionOptions] = None) -> torch.Tensor:
     """Decode attention (token i is the one new token of request i) on the tensor cores;
-    bfloat16, head_dim in TILED_HEAD_DIMS, at most 16 query heads per KV head.
+    bfloat16, head_dim in TILED_HEAD_DIMS, at most 16 query heads per KV head.  ``options``:
+    a distance bias, a sink, a gate (values of the keys' size only).
 
     ``rotary`` = (cos, sin), float32 [requests, head_dim / 2]: the rows of ``qkv`` are not
     rotated yet; the kernel rotates the query heads on the way in.  ``write_cache``: the
@@ -900,6 +921,7 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     S = qkv.shape[0]
     if block_table.shape[0] != S or positions.numel() != S:
         raise KernelError("decode attention needs one token per request")
+    opt = _tiled_options(options, S, num_heads, qkv)
     cos = sin = None
     if rotary is not None and rotary[0] is not None:
         cos, sin = rotary
@@ -926,11 +948,12 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     f = _fn("attention_bf16", "hb_attention_decode_bf16",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_void_p])
+             c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p])
     _run(f(_p(out), _p(part_o), _p(part_ml), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages),
            _p(block_table), block_table.shape[1], _p(positions), S, num_heads, num_kv_heads,
            head_dim, page_size, int(window or 0), float(scale), int(n_splits), _p(cos), _p(sin),
-           1 if write_cache else 0, int(warps), _stream()),
+           1 if write_cache else 0, int(warps), _p(opt.slopes), int(opt.sink), _p(opt.gate),
+           opt.gate_stride, _stream()),
          "attention_decode_bf16")
     return out
 
@@ -946,7 +969,8 @@ def attention_prefill_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: to
                            block_table: torch.Tensor, q_tiles: torch.Tensor,
                            cu_tokens: torch.Tensor, start_pos: torch.Tensor, num_heads: int,
                            num_kv_heads: int, head_dim: int, page_size: int,
-                           window: Optional[int], scale: float) -> torch.Tensor:
+                           window: Optional[int], scale: float,
+                           options: Optional[AttentionOptions] = None) -> torch.Tensor:
     """Attention of query-token tiles over the cache, causal by position; ``q_tiles`` is
     int32 [tiles, 2] = (request, first local token) for tiles of
     ``16 * prefill_tiling(...)[1]`` tokens."""
@@ -966,14 +990,17 @@ def attention_prefill_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: to
                           f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
     heads, subtiles = prefill_tiling(num_heads, num_kv_heads)
     T = qkv.shape[0]
+    opt = _tiled_options(options, T, num_heads, qkv)
     out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     f = _fn("attention_bf16", "hb_attention_prefill_bf16",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+             c_void_p, c_int, c_void_p, c_int, c_void_p])
     _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), _p(block_table),
            block_table.shape[1], _p(q_tiles), q_tiles.shape[0], _p(cu_tokens), _p(start_pos),
            num_heads, num_kv_heads, head_dim, heads, subtiles, page_size, int(window or 0),
-           float(scale), _stream()), "attention_prefill_bf16")
+           float(scale), _p(opt.slopes), int(opt.sink), _p(opt.gate), opt.gate_stride, _stream()),
+         "attention_prefill_bf16")
     return out
 
 
@@ -987,7 +1014,8 @@ def tc_attention_supported(num_heads: int, num_kv_heads: int, head_dim: int, pag
 def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                          block_table: torch.Tensor, q_tiles: torch.Tensor, cu_tokens: torch.Tensor,
                          start_pos: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                         page_size: int, window: Optional[int], scale: float, pairs: bool = False) -> torch.Tensor:
+                         page_size: int, window: Optional[int], scale: float, pairs: bool = False,
+                         options: Optional[AttentionOptions] = None) -> torch.Tensor:
     """Attention of query tiles over the cache on tcgen05 tensor cores; ``q_tiles`` is int32
     [tiles, 2] = (request, first local token) for tiles of ``128 // (nh // nkv)`` tokens, or
     with ``pairs`` of twice as many: then a block works on two tiles of query rows at a time
@@ -1008,14 +1036,24 @@ def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     T = qkv.shape[0]
     out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     _scratch, _tickets, err = _gemm_workspace(qkv.device)
-    f = _fn(*(("attention_pair", "hb_attention_prefill_pair") if pairs else
-              ("attention_tc", "hb_attention_prefill_tc")),
-            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p,
-             c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    common = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p,
+              c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+    if pairs:
+        if options is not None and not options.plain:
+            raise KernelError("the kernel with two query tiles a block takes no attention options")
+        f = _fn("attention_pair", "hb_attention_prefill_pair", common + [c_void_p])
+        _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table),
+               block_table.shape[1], _p(q_tiles), q_tiles.shape[0], _p(cu_tokens), _p(start_pos), num_heads,
+               num_kv_heads, head_dim, page_size, int(window or 0), float(scale), _p(err), _stream()),
+             "attention_prefill_pair")
+        return out
+    opt = _tiled_options(options, T, num_heads, qkv)
+    f = _fn("attention_tc", "hb_attention_prefill_tc", common + [c_void_p, c_int, c_void_p, c_int, c_void_p])
     _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table),
            block_table.shape[1], _p(q_tiles), q_tiles.shape[0], _p(cu_tokens), _p(start_pos), num_heads,
-           num_kv_heads, head_dim, page_size, int(window or 0), float(scale), _p(err), _stream()),
-         "attention_prefill_pair" if pairs else "attention_prefill_tc")
+           num_kv_heads, head_dim, page_size, int(window or 0), float(scale), _p(err), _p(opt.slopes),
+           int(opt.sink), _p(opt.gate), opt.gate_stride, _stream()),
+         "attention_prefill_tc")
     return out
 
 
@@ -1117,7 +1155,33 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
 def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, num_kv_heads, head_dim,
                             page_size, window, scale, options: AttentionOptions) -> torch.Tensor:
     """The kernels that take ``AttentionOptions``; q is ready and the step's keys and values
-    are in the pages (``qk_norm_kv_write``)."""
+    are in the pages (``qk_norm_kv_write``).  bfloat16 with a tiled head size and values of the
+    keys' size runs on the tensor cores as plain attention does: the split-context decode
+    kernel for steps of single tokens, the tcgen05 kernel with one tile of query rows a block
+    for portions, the ``mma.sync`` kernel for the sizes that one does not take.  Everything
+    else, and float32, runs one warp a (token, head)."""
+    if (ATTENTION_OPTIONS_TILED and qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS
+            and options.value_dim is None):
+        if ctx.decode_only and num_heads // num_kv_heads <= 16:
+            splits = ctx.extras.get("decode_splits")
+            if splits is None:
+                splits = decode_splits(ctx.num_seqs, num_kv_heads, ctx.max_context_len, head_dim)
+            return attention_decode_bf16(qkv, k_pages, v_pages, block_table, ctx.positions, num_heads,
+                                         num_kv_heads, head_dim, page_size, window, scale, splits,
+                                         None, False,
+                                         decode_warps(ctx.num_seqs * num_kv_heads, splits, head_dim,
+                                                      ctx.max_context_len), options=options)
+        if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
+                and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
+            tiles = _step_tiles(ctx, 128 // (num_heads // num_kv_heads), True, qkv.device)
+            return attention_prefill_tc(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,
+                                        ctx.start_pos, num_heads, num_kv_heads, head_dim, page_size,
+                                        window, scale, False, options=options)
+        _heads, subtiles = prefill_tiling(num_heads, num_kv_heads)
+        tiles = _step_tiles(ctx, 16 * subtiles, False, qkv.device)
+        return attention_prefill_bf16(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,
+                                      ctx.start_pos, num_heads, num_kv_heads, head_dim, page_size,
+                                      window, scale, options=options)
     return attention_generic(qkv, k_pages, v_pages, block_table, ctx.seq_of_token, ctx.positions,
                              num_heads, num_kv_heads, head_dim, page_size, window, scale, options)
 

@@ -65,8 +65,16 @@ MZ_B = _model(150, 80, 300, 3e-6, None, [
     (_attn(5, 5, 16, 16, 0.25), _moe(16, 6, 4, 0, 16)),
     (_attn(8, 2, 8, 24, 0.4, (0.1, 1)), _moe(12, 2, 2, 3, None)),
 ], loop=(0, 1, 3))
-MZ_CONFIGS = {"mz_a": MZ_A, "mz_b": MZ_B}
-MZ_SEEDS = {"mz_a": 7, "mz_b": 8}
+# Head sizes the tensor-core attention kernels take (keys and values alike): 64 on the tcgen05
+# kernel, 32 on the mma.sync one, 128 with four query heads a KV head; the loop covers the
+# last two layers.
+MZ_C = _model(180, 128, 320, 1e-5, 0.6, [
+    (_attn(4, 2, 64, 64, 0.125, (0.3, 20)), _moe(32, 4, 2, 1, 48)),
+    (_attn(2, 1, 32, 32, 0.2), None),
+    (_attn(4, 1, 128, 128, 0.09, (0.5, 9)), _moe(24, 3, 2, 2, None)),
+], loop=(1, 3, 2))
+MZ_CONFIGS = {"mz_a": MZ_A, "mz_b": MZ_B, "mz_c": MZ_C}
+MZ_SEEDS = {"mz_a": 7, "mz_b": 8, "mz_c": 10}
 # one layer each: a mechanism alone, and no loop at all
 MZ_ALONE = {
     "attention_only": _model(97, 64, 200, 1e-5, 1.0, [(_attn(4, 2, 16, 16, 0.25, (0.5, 5)), None)]),
@@ -437,11 +445,13 @@ def test_attention_far_key_page_borders_first_tokens_and_the_sink(dtype):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_attention_of_portions_behind_a_prefix_against_the_plain_softmax(dtype):
+@pytest.mark.parametrize("dtype,hd,vd", [("float32", 24, 40), ("bfloat16", 64, 64), ("bfloat16", 32, 32),
+                                         ("bfloat16", 128, 128), ("bfloat16", 64, 32)])
+def test_attention_of_portions_behind_a_prefix_against_the_plain_softmax(dtype, hd, vd):
     """Three requests in one batch: a portion of 37 tokens behind 100 cached ones, a whole
     prompt of 50, one decoded token at position 211; random keys, every row against the plain
-    scores with bias, sink and gate."""
+    scores with bias, sink and gate.  The sizes take every kernel in turn: one warp a row,
+    tcgen05, mma.sync, and one warp a row again where values are smaller than keys."""
     from types import SimpleNamespace
     from helios_b200.csrc import ops
     from helios_b200.engine.batch import SeqSlice
@@ -449,7 +459,6 @@ def test_attention_of_portions_behind_a_prefix_against_the_plain_softmax(dtype):
     dt = _dt(dtype)
     g = torch.Generator().manual_seed(5)
     page, nh, nkv = 16, 6, 2
-    hd, vd = (24, 40) if dtype == "float32" else (64, 64)
     lens, starts = [137, 50, 212], [100, 0, 211]
     slopes = pm.head_slopes(nh)
     ks = [torch.randn(n, nkv, hd, generator=g).to(dt).float() for n in lens]
@@ -496,6 +505,52 @@ def test_attention_of_portions_behind_a_prefix_against_the_plain_softmax(dtype):
         tol = 2e-5 if dtype == "float32" else 2e-2
         assert (out[o:o + counts[r]].double() - want).abs().max() < tol, r
         o += counts[r]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hd,G", [(64, 4), (128, 1), (32, 16), (96, 3)])
+def test_decode_kernel_with_its_context_in_one_slice_in_a_cluster_and_merged(hd, G):
+    """Five requests of unequal length, one token each, on the split-context decode kernel:
+    the context as one slice, as four (merged inside a thread-block cluster) and as twelve
+    (merged by a second kernel).  Bias, sink and gate are applied where the slices meet."""
+    from helios_b200.csrc import ops
+
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(8)
+    page, nkv = 16, 2
+    nh = nkv * G
+    lens = [700, 1, 17, 333, 64]
+    slopes = pm.head_slopes(nh)
+    ks = [torch.randn(n, nkv, hd, generator=g).to(dt).float() for n in lens]
+    vs = [torch.randn(n, nkv, hd, generator=g).to(dt).float() for n in lens]
+    pages_each = [-(-n // page) for n in lens]
+    total = sum(pages_each)
+    order = torch.randperm(total + 2, generator=g)[:total].to(torch.int32)
+    kp = torch.full((total + 3, nkv, page, hd), float("nan"), dtype=dt)
+    vp = torch.full((total + 3, nkv, page, hd), float("nan"), dtype=dt)
+    table = torch.full((len(lens), max(pages_each)), -1, dtype=torch.int32)
+    off = 0
+    for r, n in enumerate(lens):
+        table[r, :pages_each[r]] = order[off:off + pages_each[r]]
+        for j in range(n):
+            kp[table[r, j // page], :, j % page] = ks[r][j].to(dt)
+            vp[table[r, j // page], :, j % page] = vs[r][j].to(dt)
+        off += pages_each[r]
+    S = len(lens)
+    q = (torch.randn(S, nh, hd, generator=g) * 0.5).to(dt)
+    gate = torch.randn(S, nh, generator=g).to(dt)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    options = ops.AttentionOptions(slopes=slopes.float().cuda(), sink=True, gate=gate.cuda())
+    want = []
+    for r in range(S):
+        s = pm.attention_scores(q[r:r + 1].double(), ks[r].double().repeat_interleave(G, 1), 0.17, slopes)
+        o = torch.einsum("hij,jhd->ihd", pm.sink_softmax(s), vs[r].double().repeat_interleave(G, 1))
+        want.append(o[0] * torch.sigmoid(gate[r].double()).unsqueeze(-1))
+    want = torch.stack(want)
+    for n_splits in (1, 4, 12):
+        out = ops.attention_decode_bf16(q.view(S, nh * hd).contiguous().cuda(), kp.cuda(), vp.cuda(), table.cuda(),
+                                        pos.cuda(), nh, nkv, hd, page, None, 0.17, n_splits, options=options)
+        assert (out.float().cpu().view(S, nh, hd).double() - want).abs().max() < 2e-2, n_splits
 
 
 @pytest.mark.gpu
