@@ -311,11 +311,39 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------- another design beside the dense decoder
-def design_configs(size):
+def mizerax_configs(size):
+    """(Mizerax config.json, dense decoder config.json of equal width, heads, KV heads, layer
+    runs, vocabulary and active feed-forward size) at layer sizes of a real model.  Four layers
+    of which the two in the middle run twice (six layer runs, six caches); every layer has the
+    routed feed-forward with two experts that return their input and a shared expert."""
+    if size == "large":
+        width, heads, kv, hd, experts, top, eff, shared, vocab = 2048, 16, 4, 128, 32, 4, 2048, 2048, 32000
+    else:
+        width, heads, kv, hd, experts, top, eff, shared, vocab = 1024, 8, 2, 64, 16, 2, 2048, 2048, 32000
+    layer = {"type": "attention",
+             "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                       "q_temp": {"coef": 0.1, "every": 1024}},
+             "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "identity": 2, "top": top},
+                     "shared": {"ff": shared}}}
+    mz = {"architecture": "Mizerax", "vocab": vocab, "width": width, "max_positions": 8192,
+          "norm": {"eps": 1e-5}, "residual_mult": 0.5, "layers": [dict(layer) for _ in range(4)],
+          "loop": {"start": 1, "stop": 3, "times": 2}}
+    dense = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": vocab,
+             "hidden_size": width, "intermediate_size": top * eff + shared, "num_hidden_layers": 6,
+             "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd,
+             "max_position_embeddings": 32768, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+             "attention_bias": False, "tie_word_embeddings": True, "hidden_act": "silu",
+             "torch_dtype": "bfloat16"}
+    return mz, dense
+
+
+def design_configs(size, design="zokelix"):
     """(Zokelix config.json, dense decoder config.json of equal width, head count, layers, vocabulary
     and active feed-forward size) at layer sizes of a real model.  Six layers: attention over a
     latent cache and the gated-delta-rule mixer in the order L D L L D L, the first feed-forward
-    dense, the others routed."""
+    dense, the others routed.  ``design`` "mizerax": ``mizerax_configs``."""
+    if design == "mizerax":
+        return mizerax_configs(size)
     if size == "large":
         width, heads, hd, rank, ff, experts, top, eff, vocab = 2048, 16, 128, 512, 8192, 32, 4, 2048, 32000
     else:
@@ -343,7 +371,7 @@ def design_configs(size):
 
 
 def run_design(args):
-    """``--design zokelix``: prefill and decode throughput of the design at two size sets beside a
+    """``--design zokelix|mizerax``: prefill and decode throughput of the design at two size sets beside a
     dense decoder of equal size, and where a step's time goes, op by op (CUDA events around every
     launcher of ``ops``, steps run kernel by kernel for that table only)."""
     import torch
@@ -370,7 +398,8 @@ def run_design(args):
 
     OPS = ["linear", "linear_bf16", "linear_logits", "linear_swiglu", "add_rmsnorm", "rmsnorm_add", "glu_act",
            "embedding", "rotary_table", "attention", "latent_prepare", "head_gemm", "latent_attention",
-           "causal_conv_silu", "delta_rule", "gated_rmsnorm", "moe_topk", "moe_experts"]
+           "causal_conv_silu", "delta_rule", "gated_rmsnorm", "moe_topk", "moe_experts",
+           "add_layernorm", "qk_norm_kv_write", "add_table_rows", "cast_rows"]
 
     def op_table(core, entries_fn, reps=3):
         """milliseconds per op name over one step, run kernel by kernel (nested ops count inside
@@ -411,9 +440,9 @@ def run_design(args):
         return {k: round(v, 4) for k, v in sorted(table.items(), key=lambda kv: -kv[1])}
 
     for size in [s for s in args.design_sizes.split(",") if s]:
-        zk, dense = design_configs(size)
+        zk, dense = design_configs(size, args.design)
         res = {}
-        for label, cfg in (("zokelix", zk), ("dense", dense)):
+        for label, cfg in ((args.design, zk), ("dense", dense)):
             vocab = cfg.get("vocab") or cfg["vocab_size"]
             model = DecoderModel.from_config(cfg, seed=args.seed, dtype="bfloat16", device=dev)
             batches = [int(b) for b in args.design_batches.split(",")]
@@ -668,7 +697,7 @@ def main():
     ap.add_argument("--max-prompt", type=int, default=4096)
     ap.add_argument("--budget", type=int, default=2048, help="tokens a step (chunked prefill)")
     ap.add_argument("--new-tokens", type=int, default=256)
-    ap.add_argument("--design", default=None, choices=["zokelix"],
+    ap.add_argument("--design", default=None, choices=["zokelix", "mizerax"],
                     help="measure another design of the package beside a dense decoder of equal size "
                          "(prefill, decode, time by op) instead of the default workload")
     ap.add_argument("--design-sizes", default="small,large")

@@ -66,6 +66,9 @@ def cmd_info(args: argparse.Namespace) -> int:
         print(f"  {n} x {key}")
     if plan.position is not None:
         print(f"  positions: {type(plan.position).__name__}")
+    for prefix, stage in plan.stages.items():
+        before = [i for i, run in enumerate(plan.schedule) if run.before == prefix]
+        print(f"  between blocks: {type(stage).__name__} ({prefix}) before runs {before}")
     dtype_bytes = 4 if args.dtype == "float32" else 2
     specs, where = cache_groups_of(plan)
     per_page = bytes_per_page(plan, args.block_size, dtype_bytes)
@@ -77,7 +80,9 @@ def cmd_info(args: argparse.Namespace) -> int:
     for g, spec in enumerate(specs):
         n_ids = sum(1 for gg, _ in where.values() if gg == g)
         keeps = "every key" if spec.window is None else f"the last {spec.window} keys"
-        print(f"  group {g}: {n_ids} caches of {spec.num_kv_heads} KV heads x {spec.head_dim}, keeps {keeps}: "
+        dims = f"{spec.head_dim}" if spec.value_dim in (None, spec.head_dim) else \
+            f"{spec.head_dim} (values {spec.value_dim})"
+        print(f"  group {g}: {n_ids} caches of {spec.num_kv_heads} KV heads x {dims}, keeps {keeps}: "
               f"{per_page[g]:,} bytes a page, {pages[g]:,} pages = {pages[g] * args.block_size:,} tokens")
     full = [n for n, s in zip(pages, specs) if s.window is None]
     if full:

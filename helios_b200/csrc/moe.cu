@@ -59,12 +59,95 @@ __global__ void moe_topk_kernel(int* __restrict__ ids, float* __restrict__ weigh
   }
 }
 
+// The same choice with one warp a token, for up to 32 * MOE_PER_LANE router outputs: lane l
+// holds the scores of outputs l, l + 32, ... in registers; maximum and sum of the softmax and
+// every pick are warp reductions (a pick: the largest choice value, the lower index on a tie).
+// The sums run over the lanes' partial sums in the order of the shuffle tree, whatever the
+// batch: a token's weights depend on its own logits alone.
+constexpr int MOE_PER_LANE = 8;
+
+__global__ void __launch_bounds__(128)
+moe_topk_warp_kernel(int* __restrict__ ids, float* __restrict__ weights,
+                     const float* __restrict__ logits, const float* __restrict__ correction,
+                     int n_tokens, int experts, int top, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= n_tokens) return;
+  const float* z = logits + (size_t)t * experts;
+  float score[MOE_PER_LANE], choice[MOE_PER_LANE];
+  float zmax = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MOE_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    score[i] = e < experts ? z[e] : -INFINITY;
+    zmax = fmaxf(zmax, score[i]);
+  }
+  const bool by_logit = (kind == MOE_SIGMOID) && (correction == nullptr);
+  if (kind == MOE_SOFTMAX) {
+    zmax = warp_max(zmax);
+    float part = 0.f;
+#pragma unroll
+    for (int i = 0; i < MOE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      score[i] = e < experts ? expf(score[i] - zmax) : 0.f;
+      part += score[i];
+    }
+    const float denom = warp_sum(part);
+#pragma unroll
+    for (int i = 0; i < MOE_PER_LANE; ++i) score[i] = score[i] / denom;
+  }
+#pragma unroll
+  for (int i = 0; i < MOE_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    const float logit = score[i];
+    if (kind == MOE_SIGMOID) score[i] = 1.f / (1.f + expf(-logit));
+    choice[i] = by_logit ? logit : score[i] + ((correction && e < experts) ? correction[e] : 0.f);
+  }
+  unsigned taken = 0;        // bit i: this lane's i-th output is chosen already
+  for (int k = 0; k < top; ++k) {
+    float best = 0.f, best_score = 0.f;
+    int at = -1;
+#pragma unroll
+    for (int i = 0; i < MOE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e >= experts || (taken >> i & 1u)) continue;
+      if (at < 0 || choice[i] > best || (best != best && choice[i] == choice[i])) {
+        best = choice[i]; best_score = score[i]; at = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_score, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      // one order for all lanes, so that they end with the same pick: a number before a NaN,
+      // the larger number, and the lower index among equals (and among NaNs)
+      const bool on = ob == ob, bn = best == best;
+      const bool wins = oa >= 0 && (at < 0 || (on && !bn) ||
+                                    (on == bn && ((on && ob > best) || ((!on || ob == best) && oa < at))));
+      if (wins) { best = ob; best_score = os; at = oa; }
+    }
+    if (at >= 0 && (at & 31) == lane) taken |= 1u << (at >> 5);
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = at;
+      weights[(size_t)t * top + k] = best_score;
+    }
+  }
+}
+
 HB_EXPORT int hb_moe_topk(int* ids, float* weights, const float* logits, const float* correction,
                           int n_tokens, int experts, int top, int kind, cudaStream_t stream) {
   if (n_tokens <= 0) return HB_OK;
   if (experts <= 0 || top <= 0 || top > experts || top > MOE_MAX_TOP ||
       (kind != MOE_SIGMOID && kind != MOE_SOFTMAX))
     return HB_BAD_ARGUMENT;
+  if (experts <= 32 * MOE_PER_LANE) {
+    hb_launch(moe_topk_warp_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, ids, weights,
+              logits, correction, n_tokens, experts, top, kind);
+    return hb_check_launch();
+  }
   hb_launch(moe_topk_kernel, dim3((n_tokens + 127) / 128), dim3(128), 0, stream, ids, weights,
             logits, correction, n_tokens, experts, top, kind);
   return hb_check_launch();

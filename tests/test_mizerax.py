@@ -597,6 +597,17 @@ def test_router_and_experts_against_the_plain_functions(dtype, ff):
     want = pm.routed_ff(h.double(), Wd, "", ml)
     tol = 2e-5 if dtype == "float32" else 3e-2 * float(want.abs().max())
     assert (got - want).abs().max() < tol
+    # rows of NaN (the padding of captured steps may bring them) still yield distinct, valid ids;
+    # so do rows of equal logits (lower index first) and more router outputs than a warp has lanes
+    for n_out in (E + I, 40, 300):
+        odd = torch.zeros(3, n_out)
+        odd[0] = float("nan")
+        odd[2, 7 % n_out] = float("nan")
+        for kind in ("softmax", "sigmoid"):
+            ids3, _ = ops.moe_topk(odd.to(dev), top, kind)
+            ids3 = ids3.cpu().tolist()
+            assert all(len(set(r)) == top and all(0 <= e < n_out for e in r) for r in ids3), (n_out, kind, ids3)
+            assert ids3[1] == list(range(top))
     # the sigmoid router with a correction too, and the old form (weight on the input) still
     ids2, w2 = ops.moe_topk(logits, 2, "sigmoid", W["correction"].to(dev))
     sg = torch.sigmoid(logits.double().cpu())
