@@ -670,6 +670,84 @@ qk_norm_kv_write_kernel(T* __restrict__ rows, int ld, const int* __restrict__ po
   }
 }
 
+// The same for bfloat16 rows with 16-byte pieces: a group of hd / 8 lanes (a power of two)
+// takes one q or k head, eight values a lane, and sums the squares inside the group; the
+// blocks with blockIdx.y == 1 copy the value heads, one 16-byte piece a thread.
+template <int GROUP>
+__global__ void __launch_bounds__(128)
+qk_norm_kv_write_vec_kernel(__nv_bfloat16* __restrict__ rows, int ld, const int* __restrict__ positions,
+                            const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                            int bt_stride, __nv_bfloat16* __restrict__ k_pages,
+                            __nv_bfloat16* __restrict__ v_pages, int n_tokens, int nh, int nkv, int vd,
+                            const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                            float coef, int every, int page_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int HD = GROUP * 8;
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (blockIdx.y == 1) {                       // value heads: pieces of 8 values
+    const int per_token = nkv * (vd >> 3);
+    if (!write_cache || tid >= (long)n_tokens * per_token) return;
+    const int t = (int)(tid / per_token), piece = (int)(tid - (long)t * per_token);
+    const int g = piece / (vd >> 3), j = (piece - g * (vd >> 3)) * 8;
+    const int pos = positions[t];
+    const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+    const __nv_bfloat16* src = rows + (size_t)t * ld + (size_t)(nh + nkv) * HD + (size_t)g * vd + j;
+    __nv_bfloat16* dst = v_pages + (((size_t)page * nkv + g) * page_size + pos % page_size) * vd + j;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    return;
+  }
+  const int per_token = nh + nkv;
+  const long item = tid / GROUP;
+  const int part = (int)(tid % GROUP);
+  const bool live = item < (long)n_tokens * per_token;
+  const int t = live ? (int)(item / per_token) : 0, h = live ? (int)(item - (long)t * per_token) : 0;
+  const int pos = positions[t];
+  const bool is_q = h < nh;
+  __nv_bfloat16* x = rows + (size_t)t * ld + (size_t)h * HD + part * 8;
+  float v[8];
+  {
+    float lo[4], hi[4];
+    load4(x, lo);
+    load4(x + 4, hi);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { v[e] = lo[e]; v[4 + e] = hi[e]; }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+#pragma unroll
+  for (int o = GROUP / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (!live) return;
+  const float* w = is_q ? wq : wk;
+  float f = 1.f;
+  if (w) f = rsqrtf(ss / (float)HD + eps);
+  if (is_q && every > 0) {
+    const float temp = 1.f + coef * logf((float)((pos + 1) / every) + 1.f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float y = v[e] * f;
+      if (w) y *= w[part * 8 + e];
+      v[e] = y * temp;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float y = v[e] * f;
+      if (w) y *= w[part * 8 + e];
+      v[e] = y;
+    }
+  }
+  __nv_bfloat16* dst = x;
+  if (!is_q && write_cache) {
+    const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+    dst = k_pages + (((size_t)page * nkv + (h - nh)) * page_size + pos % page_size) * HD + part * 8;
+  }
+  float lo[4] = {v[0], v[1], v[2], v[3]}, hi[4] = {v[4], v[5], v[6], v[7]};
+  store4(dst, lo);
+  store4(dst + 4, hi);
+}
+
 HB_EXPORT int hb_qk_norm_kv_write(void* rows, int ld, const int* positions, const int* seq_of_token,
                                   const int* block_table, int bt_stride, void* k_pages, void* v_pages,
                                   int T, int nh, int nkv, int hd, int vd, const float* wq,
@@ -679,6 +757,26 @@ HB_EXPORT int hb_qk_norm_kv_write(void* rows, int ld, const int* positions, cons
   if (nh <= 0 || nkv <= 0 || hd <= 0 || vd <= 0 || page_size <= 0 || every < 0 ||
       (long)nh * hd + (long)nkv * (hd + vd) > ld)
     return HB_BAD_ARGUMENT;
+  const int group = hd / 8;
+  const bool vec = act_dt == HB_BF16 && hd % 8 == 0 && vd % 8 == 0 && ld % 8 == 0 &&
+                   (group == 4 || group == 8 || group == 16 || group == 32) &&
+                   (uintptr_t)rows % 16 == 0 && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0;
+  if (vec) {
+    const long norm_threads = (long)T * (nh + nkv) * group;
+    const long copy_threads = write_cache ? (long)T * nkv * (vd / 8) : 0;
+    const long most = norm_threads > copy_threads ? norm_threads : copy_threads;
+    dim3 grid((unsigned)((most + 127) / 128), write_cache ? 2 : 1);
+#define HB_QK_VEC(G)                                                                               \
+    hb_launch(qk_norm_kv_write_vec_kernel<G>, grid, dim3(128), 0, stream, (__nv_bfloat16*)rows, ld,   \
+              positions, seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pages,               \
+              (__nv_bfloat16*)v_pages, T, nh, nkv, vd, wq, wk, eps, coef, every, page_size, write_cache)
+    if (group == 4) HB_QK_VEC(4);
+    else if (group == 8) HB_QK_VEC(8);
+    else if (group == 16) HB_QK_VEC(16);
+    else HB_QK_VEC(32);
+#undef HB_QK_VEC
+    return hb_check_launch();
+  }
   const long items = (long)T * (nh + 2 * nkv);
   HB_DISPATCH_DTYPE(act_dt, TA,
     hb_launch(qk_norm_kv_write_kernel<TA>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (TA*)rows, ld,

@@ -307,8 +307,9 @@ def test_layer_norm_with_a_pending_sum(dtype):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_query_and_key_norm_temperature_and_the_cache_write(dtype):
+@pytest.mark.parametrize("dtype,hd,vd", [("float32", 24, 40), ("bfloat16", 24, 40), ("bfloat16", 64, 32),
+                                         ("bfloat16", 128, 128), ("bfloat16", 32, 8), ("float32", 64, 32)])
+def test_query_and_key_norm_temperature_and_the_cache_write(dtype, hd, vd):
     """Positions just below, at and above every step of the temperature (every 5: positions 3,
     4, 5, 8, 9, 10) and position 0; keys and values land at the token's place in scrambled
     pages; values of another size than keys; columns behind q | k | v stay as they were."""
@@ -316,7 +317,7 @@ def test_query_and_key_norm_temperature_and_the_cache_write(dtype):
 
     dt = _dt(dtype)
     g = torch.Generator().manual_seed(2)
-    nh, nkv, hd, vd, page, eps, coef, every = 3, 1, 24, 40, 4, 1e-5, 0.7, 5
+    nh, nkv, page, eps, coef, every = 4, 2, 4, 1e-5, 0.7, 5      # heads of 24: one warp a head; 32 to 128: 16-byte pieces
     pos = torch.tensor([0, 3, 4, 5, 8, 9, 10, 14, 15, 33], dtype=torch.int32)
     T = pos.numel()
     ld = nh * hd + nkv * (hd + vd) + 8
