@@ -385,6 +385,9 @@ def run_design(args):
     gen = torch.Generator().manual_seed(args.seed)
     page, ctx_end, prompt = 16, args.context, PREFILL_TOKENS
     out = {"design": args.design, "context": ctx_end, "prefill_tokens": prompt, "sizes": {}}
+    sampler = ClockSampler()
+    sampler.start()
+    t_begin = time.time()
 
     def timed(fn, n):
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
@@ -495,6 +498,8 @@ def run_design(args):
             del core, model
             torch.cuda.empty_cache()
         out["sizes"][size] = res
+    out["clocks"] = sampler.summary(t_begin, time.time())
+    sampler.stop()
     print(json.dumps(out))
     return 0
 

@@ -101,7 +101,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const int* __restrict__ positions, int nh, int nkv, int page_size,
                         int window, float scale_log2, int n_splits, int cluster_merge,
                         const float* __restrict__ rot_cos, const float* __restrict__ rot_sin,
-                        __nv_bfloat16* k_write, __nv_bfloat16* v_write, AttnOptions opt) {
+                        __nv_bfloat16* k_write, __nv_bfloat16* v_write, AttnOptions opt,
+                        QkPrepare prep) {
   // rot_cos / rot_sin [requests, HD / 2]: q (and the new key) still lack their rotation.
   // k_write / v_write (the cache again, writable): the new token's key and value are still
   // in the q|k|v row and go into the cache here.
@@ -211,9 +212,27 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
       const size_t dst = ((size_t)(page * nkv + kvh) * page_size + pos % page_size) * HD;
       const __nv_bfloat16* k_new = q + (size_t)seq * q_stride + (size_t)(nh + kvh) * HD;
       const __nv_bfloat16* v_new = k_new + (size_t)nkv * HD;
+      // a lane holds the pairs (j, j + 1) of both halves of the key: HD / 2 <= 64, one trip
+      float k_factor = 1.f;
+      if (prep.wk != nullptr) {
+        float ss = 0.f;
+        const int j = 2 * lane;
+        if (j < HD / 2) {
+          const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k_new + j));
+          const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k_new + j + HD / 2));
+          ss = x1.x * x1.x + x1.y * x1.y + x2.x * x2.x + x2.y * x2.y;
+        }
+        k_factor = rsqrtf(warp_sum(ss) / (float)HD + prep.eps);
+      }
       for (int j = 2 * lane; j < HD / 2; j += 64) {
-        const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k_new + j));
-        const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k_new + j + HD / 2));
+        float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k_new + j));
+        float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k_new + j + HD / 2));
+        if (prep.wk != nullptr) {
+          const float2 w1 = *reinterpret_cast<const float2*>(prep.wk + j);
+          const float2 w2 = *reinterpret_cast<const float2*>(prep.wk + j + HD / 2);
+          x1 = make_float2(x1.x * k_factor * w1.x, x1.y * k_factor * w1.y);
+          x2 = make_float2(x2.x * k_factor * w2.x, x2.y * k_factor * w2.y);
+        }
         float2 r1 = x1, r2 = x2;
         if (rot_cos != nullptr) {
           const float2 c = *reinterpret_cast<const float2*>(rot_cos + (size_t)seq * (HD / 2) + j);
@@ -248,6 +267,39 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         const int row = g0 + (e & 1) * 8;
         const int col = ks * 16 + c0 + (e >> 1) * 8;
         qa[ks][e] = (row < G) ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col) : 0u;
+      }
+    }
+    if (prep.wq != nullptr || prep.every > 0) {
+      // a head's values are spread over the four lanes of a quad: rows g0 (e even) and g0 + 8
+      float ss[2] = {0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qa[ks][e]));
+          ss[e & 1] += x.x * x.x + x.y * x.y;
+        }
+      }
+      float inv_rms[2];
+      const float temp = prep.every > 0 ? 1.f + prep.coef * logf((float)((pos + 1) / prep.every) + 1.f) : 1.f;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], 1);
+        ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], 2);
+        inv_rms[r] = prep.wq != nullptr ? rsqrtf(ss[r] / (float)HD + prep.eps) : 1.f;
+      }
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = ks * 16 + c0 + (e >> 1) * 8;
+          const float2 w = prep.wq != nullptr ? *reinterpret_cast<const float2*>(prep.wq + col) : make_float2(1.f, 1.f);
+          const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qa[ks][e]));
+          // the norm, the weight, then the temperature: the order of the kernel that does this alone
+          const float f = inv_rms[e & 1];
+          __nv_bfloat162 y = __floats2bfloat162_rn(x.x * f * w.x * temp, x.y * f * w.y * temp);
+          qa[ks][e] = *reinterpret_cast<uint32_t*>(&y);
+        }
       }
     }
     if (rot_cos != nullptr) {
@@ -607,7 +659,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
                   const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                   const int* positions, int S, int nh, int nkv, int page_size, int window,
                   float scale, int n_splits, const float* rot_cos, const float* rot_sin,
-                  int write_cache, AttnOptions opt, cudaStream_t stream) {
+                  int write_cache, AttnOptions opt, QkPrepare prep, cudaStream_t stream) {
   constexpr int RS = HD + 8;
   // the new keys and values go into the very pages the kernel reads
   __nv_bfloat16* k_write = write_cache ? (__nv_bfloat16*)const_cast<void*>(k_pages) : nullptr;
@@ -643,14 +695,14 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
     cudaLaunchKernelEx(&cfg, kernel, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
                        positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 1,
-                       rot_cos, rot_sin, k_write, v_write, opt);
+                       rot_cos, rot_sin, k_write, v_write, opt, prep);
     return hb_check_launch();
   }
   hb_launch(kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 
       (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
       positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 0,
-      rot_cos, rot_sin, k_write, v_write, opt);
+      rot_cos, rot_sin, k_write, v_write, opt, prep);
   if (n_splits > 1)
     hb_launch(decode_merge_kernel<HD>, dim3(S * nh), dim3(HD < 128 ? HD : 128), 0, stream, 
         (__nv_bfloat16*)out, part_o, part_ml, n_splits, nh, opt);
@@ -738,9 +790,14 @@ HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml,
                                        float scale, int n_splits, const float* rot_cos,
                                        const float* rot_sin, int write_cache, int warps,
                                        const float* slopes, int sink, const void* gate,
-                                       int gate_stride, cudaStream_t stream) {
+                                       int gate_stride, const float* norm_wq, const float* norm_wk,
+                                       float norm_eps, float temp_coef, int temp_every,
+                                       cudaStream_t stream) {
   if (S <= 0) return HB_OK;
   const AttnOptions opt = {slopes, (const __nv_bfloat16*)gate, gate_stride, sink};
+  const QkPrepare prep = {norm_wq, norm_wk, norm_eps, temp_coef, temp_every};
+  if ((norm_wq == nullptr) != (norm_wk == nullptr) || temp_every < 0) return HB_BAD_ARGUMENT;
+  if (norm_wk != nullptr && !write_cache) return HB_BAD_ARGUMENT;     // a cached key is normed already
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || page_size <= 0 || n_splits < 1 ||
       (warps != 4 && warps != 8))
     return HB_BAD_ARGUMENT;
@@ -751,7 +808,7 @@ HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml,
   HB_DISPATCH_HD(hd, return (launch_decode<HD, W>(out, part_o, part_ml, q, q_stride, k_pages, v_pages, \
                                                   block_table, bt_stride, positions, S, nh, nkv,      \
                                                   page_size, window, scale, n_splits, rot_cos,        \
-                                                  rot_sin, write_cache, opt, stream)))
+                                                  rot_sin, write_cache, opt, prep, stream)))
   if (warps == 8) HB_DECODE(8);
   HB_DECODE(4);
 #undef HB_DECODE

@@ -33,3 +33,16 @@ __device__ __forceinline__ float attn_gate_factor(const AttnOptions& opt, size_t
   const float g = __bfloat162float(opt.gate[token * (size_t)opt.gate_stride + head]);
   return 1.f / (1.f + __expf(-g));
 }
+
+// What a decode kernel that takes the step's q | k | v rows straight from the projection does
+// to them on the way in, beside (or instead of) a rotation: q and k heads divided by their
+// root mean square (eps inside the root) and multiplied by a weight per channel (wq, wk: float
+// [head_dim], one for all heads; null: no norm), the query also by
+// 1 + coef * ln(floor((position + 1) / every) + 1) (every 0: no such factor).
+struct QkPrepare {
+  const float* wq;
+  const float* wk;
+  float eps;
+  float coef;
+  int every;
+};

@@ -894,7 +894,7 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
                           num_kv_heads: int, head_dim: int, page_size: int,
                           window: Optional[int], scale: float, n_splits: int,
                           rotary=None, write_cache: bool = False, warps: Optional[int] = None,
-                          options: Optional[AttentionOptions] = None) -> torch.Tensor:
+                          options: Optional[AttentionOptions] = None, qk_norm=None) -> torch.Tensor:
     """Decode attention (token i is the one new token of request i) on the tensor cores;
     bfloat16, head_dim in TILED_HEAD_DIMS, at most 16 query heads per KV head.  ``options``:
     a distance bias, a sink, a gate (values of the keys' size only).
@@ -903,7 +903,9 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     rotated yet; the kernel rotates the query heads on the way in.  ``write_cache``: the
     requests' new keys (rotated likewise) and values are still in ``qkv`` and the kernel
     stores them in the pages before it attends.  (Without either, ``rope_kv_write`` must have
-    run.)  ``qkv`` itself is left as it was.  ``warps``: 4 (the default) or 8 warps a block
+    run.)  ``qk_norm`` = (q weight, k weight, eps, temperature coefficient, temperature period):
+    what ``qk_norm_kv_write`` does to q and k, done on the way in (needs ``write_cache``; rows may
+    be wider than q | k | v).  ``qkv`` itself is left as it was.  ``warps``: 4 (the default) or 8 warps a block
     (``decode_warps``)."""
     _check(qkv, "qkv", torch.bfloat16, 2)
     _check(k_pages, "k_pages", torch.bfloat16, 4)
@@ -930,7 +932,22 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
         if tuple(cos.shape) != (S, head_dim // 2) or cos.shape != sin.shape \
                 or not (cos.is_contiguous() and sin.is_contiguous()):
             raise KernelError(f"rotary tables have shape {tuple(cos.shape)}, expected ({S}, {head_dim // 2})")
-    if (cos is not None or write_cache) and (qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim
+    wq = wk = None
+    n_eps, t_coef, t_every = 0.0, 0.0, 0
+    if qk_norm is not None:
+        wq, wk, n_eps, t_coef, t_every = qk_norm
+        if not write_cache:
+            raise KernelError("q/k norm inside the decode kernel goes with the cache write")
+        for name, w in (("q norm weight", wq), ("k norm weight", wk)):
+            if w is not None:
+                _check(w, name, torch.float32, 1)
+                if w.numel() != head_dim:
+                    raise KernelError(f"{name} has {w.numel()} entries for heads of {head_dim}")
+        if (wq is None) != (wk is None):
+            raise KernelError("query and key norm come together")
+    exact = qk_norm is None            # rows of a fused projection may carry more columns behind q | k | v
+    if (cos is not None or write_cache) and ((qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim if exact
+                                              else qkv.shape[1] < (num_heads + 2 * num_kv_heads) * head_dim)
                                              or not qkv.is_contiguous()):
         raise KernelError(f"q|k|v rows have {qkv.shape[1]} entries for {num_heads} + 2 x {num_kv_heads} "
                           f"heads of {head_dim}")
@@ -948,12 +965,13 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     f = _fn("attention_bf16", "hb_attention_decode_bf16",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
-             c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p])
+             c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int,
+             c_void_p])
     _run(f(_p(out), _p(part_o), _p(part_ml), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages),
            _p(block_table), block_table.shape[1], _p(positions), S, num_heads, num_kv_heads,
            head_dim, page_size, int(window or 0), float(scale), int(n_splits), _p(cos), _p(sin),
            1 if write_cache else 0, int(warps), _p(opt.slopes), int(opt.sink), _p(opt.gate),
-           opt.gate_stride, _stream()),
+           opt.gate_stride, _p(wq), _p(wk), float(n_eps), float(t_coef), int(t_every), _stream()),
          "attention_decode_bf16")
     return out
 
@@ -1098,7 +1116,7 @@ def _step_tiles(ctx, tile: int, longest_first: bool, device) -> torch.Tensor:
 def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
               page_size: int, window: Optional[int], scale: float,
-              fresh=None, options: Optional[AttentionOptions] = None) -> torch.Tensor:
+              fresh=None, options: Optional[AttentionOptions] = None, prepare=None) -> torch.Tensor:
     """Attention of the step's tokens over the cache; chooses the kernel by dtype, sizes
     and the shape of the batch described by ``ctx``.  bfloat16 with a tiled head size
     runs on the tensor cores (split-context decode kernel for batches of single tokens,
@@ -1108,10 +1126,13 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     are rotated (tables None: no rotation) and, with ``write_cache``, k and v stored in the
     pages first: inside the decode kernel where that one runs, else by ``rope_kv_write``.
 
-    ``options`` (``AttentionOptions``): a distance bias, a sink, a gate, values of another size."""
-    if options is not None and not options.plain:
+    ``options`` (``AttentionOptions``): a distance bias, a sink, a gate, values of another size.
+    ``prepare`` = (q weight, k weight, eps, temperature coefficient, temperature period,
+    write_cache), with ``options`` only: ``qkv`` comes straight from a fused projection and still
+    wants ``qk_norm_kv_write``: inside the decode kernel where that one runs, else as a launch."""
+    if prepare is not None or (options is not None and not options.plain):
         return _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, num_kv_heads,
-                                       head_dim, page_size, window, scale, options)
+                                       head_dim, page_size, window, scale, options or _NO_OPTIONS, prepare)
     decode = (qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS and ctx.decode_only
               and num_heads // num_kv_heads <= 16)
     rotary, write_cache = None, False
@@ -1152,25 +1173,41 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                              num_heads, num_kv_heads, head_dim, page_size, window, scale)
 
 
+#: steps of single tokens: q/k norm, temperature and cache write inside the decode kernel
+ATTENTION_DECODE_QK_NORM = True
+
+
 def _attention_with_options(ctx, qkv, k_pages, v_pages, block_table, num_heads, num_kv_heads, head_dim,
-                            page_size, window, scale, options: AttentionOptions) -> torch.Tensor:
-    """The kernels that take ``AttentionOptions``; q is ready and the step's keys and values
-    are in the pages (``qk_norm_kv_write``).  bfloat16 with a tiled head size and values of the
+                            page_size, window, scale, options: AttentionOptions, prepare=None) -> torch.Tensor:
+    """The kernels that take ``AttentionOptions``.  Without ``prepare`` q is ready and the
+    step's keys and values are in the pages; with it (see ``attention``) that is done here first,
+    by ``qk_norm_kv_write`` or by the decode kernel itself.  bfloat16 with a tiled head size and values of the
     keys' size runs on the tensor cores as plain attention does: the split-context decode
     kernel for steps of single tokens, the tcgen05 kernel with one tile of query rows a block
     for portions, the ``mma.sync`` kernel for the sizes that one does not take.  Everything
     else, and float32, runs one warp a (token, head)."""
-    if (ATTENTION_OPTIONS_TILED and qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS
-            and options.value_dim is None):
-        if ctx.decode_only and num_heads // num_kv_heads <= 16:
+    tiled = (ATTENTION_OPTIONS_TILED and qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS
+             and options.value_dim is None)
+    decode = tiled and ctx.decode_only and num_heads // num_kv_heads <= 16
+    fused = None
+    if prepare is not None:
+        wq, wk, eps, coef, every, write = prepare
+        if decode and write and ATTENTION_DECODE_QK_NORM and qkv.is_contiguous():
+            fused = (wq, wk, eps, coef, every)
+        else:
+            qk_norm_kv_write(qkv, ctx.positions, ctx.seq_of_token, block_table, k_pages, v_pages, num_heads,
+                             num_kv_heads, head_dim, options.value_dim or head_dim, page_size, wq, wk, eps,
+                             coef, every, write_cache=write)
+    if tiled:
+        if decode:
             splits = ctx.extras.get("decode_splits")
             if splits is None:
                 splits = decode_splits(ctx.num_seqs, num_kv_heads, ctx.max_context_len, head_dim)
             return attention_decode_bf16(qkv, k_pages, v_pages, block_table, ctx.positions, num_heads,
                                          num_kv_heads, head_dim, page_size, window, scale, splits,
-                                         None, False,
+                                         None, fused is not None,
                                          decode_warps(ctx.num_seqs * num_kv_heads, splits, head_dim,
-                                                      ctx.max_context_len), options=options)
+                                                      ctx.max_context_len), options=options, qk_norm=fused)
         if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
                 and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
             tiles = _step_tiles(ctx, 128 // (num_heads // num_kv_heads), True, qkv.device)

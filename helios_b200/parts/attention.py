@@ -130,9 +130,10 @@ class SinkGQAAttention(Mixer):
     heads (``qk_norm``); temp(p) = 1 + coef * ln(floor((p + 1) / every) + 1)
     (``q_temperature`` = (coef, every) or None); slope_h from ``slopes`` (a list, one a head, or
     None).  Values may have another size than keys (``value_dim``).  Every option can be left
-    out; the constants are the caller's.  One fused projection gives q | k | v | gate; one
-    kernel norms q and k and writes k and v into the request's pages; the gate is applied
-    where attention writes its output."""
+    out; the constants are the caller's.  One fused projection gives q | k | v | gate; q and
+    k are normed and k and v written into the request's pages by one launch before attention,
+    or, in steps of single tokens, inside the decode kernel; the gate is applied where
+    attention writes its output."""
 
     def __init__(self, width: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  value_dim: Optional[int] = None, qk_norm: bool = True, eps: float = 1e-6,
@@ -202,16 +203,13 @@ class SinkGQAAttention(Mixer):
         rows = ops.linear(x, self.w_in)
         table = ctx.block_tables[cache.group]
         coef, every = self.q_temperature or (0.0, 0)
-        ops.qk_norm_kv_write(rows, ctx.positions, ctx.seq_of_token, table, cache.k_pages, cache.v_pages,
-                             self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim,
-                             cache.page_size, self.q_weight, self.k_weight, self.eps, coef, every,
-                             write_cache=cache.write)
         gate = rows[:, self._gate_col:self._gate_col + self.num_heads] if self.head_gate else None
         options = ops.AttentionOptions(slopes=self.slopes, sink=self.sink, gate=gate,
                                        value_dim=None if self.value_dim == self.head_dim else self.value_dim)
         attn = ops.attention(ctx, rows, cache.k_pages, cache.v_pages, table, self.num_heads,
                              self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale,
-                             options=options)
+                             options=options,
+                             prepare=(self.q_weight, self.k_weight, self.eps, coef, every, cache.write))
         return ops.linear(attn, self.w_o)
 
 

@@ -555,6 +555,56 @@ def test_decode_kernel_with_its_context_in_one_slice_in_a_cluster_and_merged(hd,
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("hd,G,every", [(64, 2, 5), (128, 4, 0), (32, 9, 1), (96, 1, 300)])
+def test_decode_kernel_norms_and_writes_on_the_way_in(hd, G, every):
+    """The decode kernel given rows straight from the projection (q | k | v | gate) does what
+    the launch before it would have done: q and k normed, the temperature on q, the new key
+    and value in the pages.  Against that launch followed by the same kernel; positions on
+    both sides of a page border and of a step of the temperature."""
+    from helios_b200.csrc import ops
+
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(11)
+    page, nkv = 16, 2
+    nh = nkv * G
+    pos = torch.tensor([0, 15, 16, 4, 5, 299, 300, 47], dtype=torch.int32)
+    S = pos.numel()
+    pages_each = [int(p) // page + 1 for p in pos]
+    total = sum(pages_each)
+    order = torch.randperm(total + 2, generator=g)[:total].to(torch.int32)
+    kp = (torch.randn(total + 3, nkv, page, hd, generator=g) * 0.5).to(dt)
+    vp = torch.randn(total + 3, nkv, page, hd, generator=g).to(dt)
+    table = torch.full((S, max(pages_each)), -1, dtype=torch.int32)
+    off = 0
+    for r in range(S):
+        table[r, :pages_each[r]] = order[off:off + pages_each[r]]
+        off += pages_each[r]
+    ld = (nh + 2 * nkv) * hd + 8 * (-(-nh // 8))
+    rows = torch.randn(S, ld, generator=g).to(dt)
+    wq, wk = torch.rand(hd, generator=g) + 0.5, torch.rand(hd, generator=g) + 0.5
+    slopes = pm.head_slopes(nh).float().cuda()
+    seq = torch.arange(S, dtype=torch.int32).cuda()
+
+    def options(r):
+        return ops.AttentionOptions(slopes=slopes, sink=True, gate=r[:, (nh + 2 * nkv) * hd:(nh + 2 * nkv) * hd + nh])
+
+    r1, k1, v1 = rows.cuda().clone(), kp.cuda().clone(), vp.cuda().clone()
+    ops.qk_norm_kv_write(r1, pos.cuda(), seq, table.cuda(), k1, v1, nh, nkv, hd, hd, page, wq.cuda(), wk.cuda(),
+                         1e-5, 0.6, every)
+    want = ops.attention_decode_bf16(r1, k1, v1, table.cuda(), pos.cuda(), nh, nkv, hd, page, None, 0.2, 2,
+                                     options=options(r1))
+    for n_splits in (1, 3):
+        r2, k2, v2 = rows.cuda().clone(), kp.cuda().clone(), vp.cuda().clone()
+        got = ops.attention_decode_bf16(r2, k2, v2, table.cuda(), pos.cuda(), nh, nkv, hd, page, None, 0.2, n_splits,
+                                        write_cache=True, options=options(r2),
+                                        qk_norm=(wq.cuda(), wk.cuda(), 1e-5, 0.6, every))
+        assert torch.equal(r2.cpu(), rows)                                   # the rows are left as they were
+        assert torch.equal(v2.cpu(), v1.cpu())
+        assert (k2.float() - k1.float()).abs().max() <= 0.02 * float(k1.float().abs().max())
+        assert (got.float() - want.float()).abs().max() < 2e-2 * max(1.0, float(want.float().abs().max()))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("ff", [40, 20])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_router_and_experts_against_the_plain_functions(dtype, ff):
