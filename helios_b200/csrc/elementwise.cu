@@ -546,6 +546,89 @@ add_layernorm_kernel(TA* __restrict__ out, float* __restrict__ residual, const T
   }
 }
 
+// The same with the row in registers (four values a thread and group, rows of whole groups up
+// to 8,192 wide): every load is on its way before the first use, so a row costs one trip to
+// memory.  The sums run thread by thread, then over the block in its fixed order, as above.
+template <typename TA>
+__global__ void __launch_bounds__(NORM_THREADS)
+add_layernorm_vec_kernel(TA* __restrict__ out, float* __restrict__ residual, const TA* __restrict__ a,
+                         const float* __restrict__ sa, const TA* __restrict__ b,
+                         const float* __restrict__ sb, float mult, const float* __restrict__ weight,
+                         const float* __restrict__ bias, const int* __restrict__ rows, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* res = residual + (size_t)r * H;
+  const TA* ar = a ? a + (size_t)r * H : nullptr;
+  const TA* br = b ? b + (size_t)r * H : nullptr;
+  const bool write_back = (rows == nullptr) && (ar != nullptr || br != nullptr);
+  float v[NORM_GROUPS][4];
+#pragma unroll
+  for (int g = 0; g < NORM_GROUPS; ++g) {
+    const int c = (g * NORM_THREADS + threadIdx.x) * 4;
+    if (c < H) load4(res + c, v[g]);
+  }
+  if (ar || br) {
+#pragma unroll
+    for (int g = 0; g < NORM_GROUPS; ++g) {
+      const int c = (g * NORM_THREADS + threadIdx.x) * 4;
+      if (c < H) {
+        float add[4] = {0.f, 0.f, 0.f, 0.f};
+        if (ar) {
+          float x[4], s4[4] = {1.f, 1.f, 1.f, 1.f};
+          load4(ar + c, x);
+          if (sa) load4(sa + c, s4);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) add[e] = s4[e] * x[e];
+        }
+        if (br) {
+          float x[4], s4[4] = {1.f, 1.f, 1.f, 1.f};
+          load4(br + c, x);
+          if (sb) load4(sb + c, s4);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) add[e] = fmaf(s4[e], x[e], add[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[g][e] = fmaf(mult, add[e], v[g][e]);
+        if (write_back) store4(res + c, v[g]);
+      }
+    }
+  }
+  if (out == nullptr) return;
+  float sum = 0.f;
+#pragma unroll
+  for (int g = 0; g < NORM_GROUPS; ++g) {
+    const int c = (g * NORM_THREADS + threadIdx.x) * 4;
+    if (c < H) sum += (v[g][0] + v[g][1]) + (v[g][2] + v[g][3]);
+  }
+  const float mean = block_sum(sum, scratch) / (float)H;
+  float sq = 0.f;
+#pragma unroll
+  for (int g = 0; g < NORM_GROUPS; ++g) {
+    const int c = (g * NORM_THREADS + threadIdx.x) * 4;
+    if (c < H) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float d = v[g][e] - mean; sq = fmaf(d, d, sq); }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(sq, scratch) / (float)H + eps);
+  TA* o = out + (size_t)i * H;
+#pragma unroll
+  for (int g = 0; g < NORM_GROUPS; ++g) {
+    const int c = (g * NORM_THREADS + threadIdx.x) * 4;
+    if (c < H) {
+      float w[4], bb[4] = {0.f, 0.f, 0.f, 0.f}, y[4];
+      load4(weight + c, w);
+      if (bias) load4(bias + c, bb);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[e] = (v[g][e] - mean) * rstd * w[e] + bb[e];
+      store4(o + c, y);
+    }
+  }
+}
+
 HB_EXPORT int hb_add_layernorm(void* out, float* residual, const void* a, const float* sa,
                                const void* b, const float* sb, float mult, const float* weight,
                                const float* bias, const int* rows, int n_out, int H, float eps,
@@ -553,6 +636,16 @@ HB_EXPORT int hb_add_layernorm(void* out, float* residual, const void* a, const 
   if (n_out <= 0) return HB_OK;
   const size_t smem = (size_t)H * sizeof(float);
   if (H <= 0 || smem > 200 * 1024) return HB_BAD_ARGUMENT;
+  const bool vec = (H % 4 == 0) && H <= NORM_THREADS * NORM_GROUPS * 4 && ((uintptr_t)out % 16 == 0) &&
+                   ((uintptr_t)residual % 16 == 0) && ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) &&
+                   ((uintptr_t)sa % 16 == 0) && ((uintptr_t)sb % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
+                   ((uintptr_t)bias % 16 == 0);
+  if (vec) {
+    HB_DISPATCH_DTYPE(act_dt, TA,
+      hb_launch(add_layernorm_vec_kernel<TA>, dim3(n_out), dim3(NORM_THREADS), 0, stream, (TA*)out, residual,
+                (const TA*)a, sa, (const TA*)b, sb, mult, weight, bias, rows, H, eps));
+    return hb_check_launch();
+  }
   HB_DISPATCH_DTYPE(act_dt, TA,
     if (smem > 40 * 1024)
       cudaFuncSetAttribute(add_layernorm_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -19,6 +19,33 @@
 #include "common.cuh"
 
 constexpr int MOE_MAX_TOP = 16;
+
+// four consecutive values as floats (float32: one 16-byte access; bfloat16: one of 8 bytes)
+template <typename T>
+__device__ __forceinline__ void moe_load4(const T* p, float (&f)[4]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    f[0] = x.x; f[1] = x.y; f[2] = x.z; f[3] = x.w;
+  } else {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&x.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+    f[0] = __low2float(a); f[1] = __high2float(a); f[2] = __low2float(b); f[3] = __high2float(b);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void moe_store4(T* p, const float (&f)[4]) {
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  } else {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    uint2 x;
+    x.x = *reinterpret_cast<uint32_t*>(&a);
+    x.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = x;
+  }
+}
+
 enum { MOE_SIGMOID = 0, MOE_SOFTMAX = 1 };
 enum { MOE_GATE_SILU = 0, MOE_GATE_CLAMPED_SWISH = 2 };     // the codes of the gated activations
 
@@ -317,6 +344,13 @@ __global__ void moe_scatter_rows_kernel(T* __restrict__ rows, const T* __restric
   const T* src = h + (size_t)(pair / top) * width;
   T* dst = rows + (size_t)place[pair] * width;
   if (weights == nullptr) {
+    // a plain copy: 16-byte pieces where rows are made of them
+    constexpr int PER = 16 / (int)sizeof(T);
+    if (width % PER == 0 && ((uintptr_t)src % 16) == 0 && ((uintptr_t)dst % 16) == 0) {
+      for (int c = threadIdx.x; c < width / PER; c += blockDim.x)
+        reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+      return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
     return;
   }
@@ -345,17 +379,63 @@ __global__ void moe_gather_sum_kernel(T* __restrict__ out, const T* __restrict__
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
+  // where every choice's row lies and what it weighs, once; then the columns
+  __shared__ const T* src[MOE_MAX_TOP];
+  __shared__ float wgt[MOE_MAX_TOP];
+  if (threadIdx.x < top) {
+    const int pair = t * top + threadIdx.x;
+    const bool same = ids != nullptr && ids[pair] >= n_real;
+    src[threadIdx.x] = same ? h + (size_t)t * width : rows + (size_t)place[pair] * width;
+    wgt[threadIdx.x] = weights ? weights[pair] : 1.f;
+  }
+  __syncthreads();
+  const bool weighted = weights != nullptr;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float a = 0.f;
     for (int k = 0; k < top; ++k) {
-      const int pair = t * top + k;
-      const bool same = ids != nullptr && ids[pair] >= n_real;
-      const float y = same ? to_float(h[(size_t)t * width + c])
-                           : to_float(rows[(size_t)place[pair] * width + c]);
-      a = weights ? fmaf(weights[pair], y, a) : a + y;
+      const float y = to_float(src[k][c]);
+      a = weighted ? fmaf(wgt[k], y, a) : a + y;
     }
     if (base) a += to_float(base[(size_t)t * width + c]);
     out[(size_t)t * width + c] = from_float<T>(a);
+  }
+}
+
+// The same with four columns a thread (rows of whole 8- or 16-byte pieces): the loads of all
+// choices are on their way before the first sum.
+template <typename T>
+__global__ void moe_gather_sum_vec_kernel(T* __restrict__ out, const T* __restrict__ rows,
+                                          const int* __restrict__ place, const int* __restrict__ ids,
+                                          const float* __restrict__ weights, const T* __restrict__ h,
+                                          const T* __restrict__ base, int n_real, int top, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  __shared__ const T* src[MOE_MAX_TOP];
+  __shared__ float wgt[MOE_MAX_TOP];
+  if (threadIdx.x < top) {
+    const int pair = t * top + threadIdx.x;
+    const bool same = ids != nullptr && ids[pair] >= n_real;
+    src[threadIdx.x] = same ? h + (size_t)t * width : rows + (size_t)place[pair] * width;
+    wgt[threadIdx.x] = weights ? weights[pair] : 1.f;
+  }
+  __syncthreads();
+  const bool weighted = weights != nullptr;
+  for (int c = threadIdx.x * 4; c < width; c += blockDim.x * 4) {
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top; ++k) {
+      float y[4];
+      moe_load4(src[k] + c, y);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[e] = weighted ? fmaf(wgt[k], y[e], a[e]) : a[e] + y[e];
+    }
+    if (base) {
+      float y[4];
+      moe_load4(base + (size_t)t * width + c, y);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[e] += y[e];
+    }
+    moe_store4(out + (size_t)t * width + c, a);
   }
 }
 
@@ -364,8 +444,13 @@ HB_EXPORT int hb_moe_gather_sum(void* out, const void* rows, const int* place, c
                                 int n_tokens, int top, int width, int act_dt, cudaStream_t stream) {
   if (n_tokens <= 0) return HB_OK;
   if (ids != nullptr && h == nullptr) return HB_BAD_ARGUMENT;
+  if (top > MOE_MAX_TOP) return HB_BAD_ARGUMENT;
+  const bool vec = width % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)rows % 16 == 0 &&
+                   (uintptr_t)h % 16 == 0 && (uintptr_t)base % 16 == 0;
   HB_DISPATCH_DTYPE(act_dt, TA,
-    hb_launch(moe_gather_sum_kernel<TA>, dim3(n_tokens), dim3(256), 0, stream, (TA*)out,
-              (const TA*)rows, place, ids, weights, (const TA*)h, (const TA*)base, n_real, top, width));
+    if (vec) hb_launch(moe_gather_sum_vec_kernel<TA>, dim3(n_tokens), dim3(256), 0, stream, (TA*)out,
+                       (const TA*)rows, place, ids, weights, (const TA*)h, (const TA*)base, n_real, top, width);
+    else hb_launch(moe_gather_sum_kernel<TA>, dim3(n_tokens), dim3(256), 0, stream, (TA*)out,
+                   (const TA*)rows, place, ids, weights, (const TA*)h, (const TA*)base, n_real, top, width));
   return hb_check_launch();
 }

@@ -281,7 +281,7 @@ def test_layer_norm_with_a_pending_sum(dtype):
 
     dt = _dt(dtype)
     g = torch.Generator().manual_seed(1)
-    for n, H in ((7, 96), (3, 50), (2, 1030)):
+    for n, H in ((7, 96), (3, 50), (2, 1030), (5, 2048), (2, 8200)):   # in registers, or through shared memory
         x = torch.randn(n, H, generator=g) * 3 + 1.5
         a, b = torch.randn(n, H, generator=g).to(dt), torch.randn(n, H, generator=g).to(dt)
         sa, sb = torch.rand(H, generator=g) + 0.5, torch.rand(H, generator=g) - 0.5
