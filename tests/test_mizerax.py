@@ -73,8 +73,15 @@ MZ_C = _model(180, 128, 320, 1e-5, 0.6, [
     (_attn(2, 1, 32, 32, 0.2), None),
     (_attn(4, 1, 128, 128, 0.09, (0.5, 9)), _moe(24, 3, 2, 2, None)),
 ], loop=(1, 3, 2))
-MZ_CONFIGS = {"mz_a": MZ_A, "mz_b": MZ_B, "mz_c": MZ_C}
-MZ_SEEDS = {"mz_a": 7, "mz_b": 8, "mz_c": 10}
+# A width that is no multiple of 4 (no 8- or 16-byte rows anywhere), three query heads on one KV
+# head, a loop of ONE pass over both layers (the input mix still runs, once), two of 3 + 1 router
+# outputs.
+MZ_D = _model(131, 50, 270, 2e-6, 1.3, [
+    (_attn(3, 1, 20, 12, 0.22, (0.8, 11)), _moe(20, 3, 2, 1, 12)),
+    (_attn(2, 2, 10, 30, 0.3), _moe(12, 2, 1, 1, None)),
+], loop=(0, 2, 1))
+MZ_CONFIGS = {"mz_a": MZ_A, "mz_b": MZ_B, "mz_c": MZ_C, "mz_d": MZ_D}
+MZ_SEEDS = {"mz_a": 7, "mz_b": 8, "mz_c": 10, "mz_d": 12}
 # one layer each: a mechanism alone, and no loop at all
 MZ_ALONE = {
     "attention_only": _model(97, 64, 200, 1e-5, 1.0, [(_attn(4, 2, 16, 16, 0.25, (0.5, 5)), None)]),
