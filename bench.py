@@ -315,7 +315,7 @@ def mizerax_configs(size):
     """(Mizerax config.json, dense decoder config.json of equal width, heads, KV heads, layer
     runs, vocabulary and active feed-forward size) at layer sizes of a real model.  Four layers
     of which the two in the middle run twice (six layer runs, six caches); every layer has the
-    routed feed-forward with two experts that return their input and a shared expert."""
+    routed feed-forward with one expert that returns its input and a shared expert."""
     if size == "large":
         width, heads, kv, hd, experts, top, eff, shared, vocab = 2048, 16, 4, 128, 32, 4, 2048, 2048, 32000
     else:
@@ -323,10 +323,10 @@ def mizerax_configs(size):
     layer = {"type": "attention",
              "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
                        "q_temp": {"coef": 0.1, "every": 1024}},
-             "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "identity": 2, "top": top},
+             "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "identity": 1, "top": top},
                      "shared": {"ff": shared}}}
     mz = {"architecture": "Mizerax", "vocab": vocab, "width": width, "max_positions": 8192,
-          "norm": {"eps": 1e-5}, "residual_mult": 0.5, "layers": [dict(layer) for _ in range(4)],
+          "norm": {"eps": 1e-5}, "residual_mult": 0.7, "layers": [dict(layer) for _ in range(4)],
           "loop": {"start": 1, "stop": 3, "times": 2}}
     dense = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": vocab,
              "hidden_size": width, "intermediate_size": top * eff + shared, "num_hidden_layers": 6,

@@ -84,7 +84,7 @@ def _toy_config(sizes):
              "router": {"experts": 4, "identity": 1, "top": 2}, "shared": {"ff": max(8, inner // 2)}}
         layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
     cfg = {"architecture": "Mizerax", "vocab": sizes["vocab_size"], "width": width,
-           "max_positions": sizes["max_pos"], "norm": {"eps": sizes["rms_eps"]}, "residual_mult": 0.5,
+           "max_positions": sizes["max_pos"], "norm": {"eps": sizes["rms_eps"]}, "residual_mult": 0.8,
            "layers": layers}
     if n >= 3:
         cfg["loop"] = {"start": 1, "stop": n - 1, "times": 2}

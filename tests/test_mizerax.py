@@ -66,10 +66,10 @@ MZ_B = _model(150, 80, 300, 3e-6, None, [
     (_attn(8, 2, 8, 24, 0.4, (0.1, 1)), _moe(12, 2, 2, 3, None)),
 ], loop=(0, 1, 3))
 # Head sizes the tensor-core attention kernels take (keys and values alike): 64 on the tcgen05
-# kernel, 32 on the mma.sync one, 128 with four query heads a KV head; the loop covers the
-# last two layers.
+# kernel with three query heads a KV head, 32 on the mma.sync one, 128 with four query heads a KV
+# head; the loop covers the last two layers.
 MZ_C = _model(180, 128, 320, 1e-5, 0.6, [
-    (_attn(4, 2, 64, 64, 0.125, (0.3, 20)), _moe(32, 4, 2, 1, 48)),
+    (_attn(6, 2, 64, 64, 0.11, (0.35, 20)), _moe(32, 4, 2, 1, 48)),
     (_attn(2, 1, 32, 32, 0.2), None),
     (_attn(4, 1, 128, 128, 0.09, (0.5, 9)), _moe(24, 3, 2, 2, None)),
 ], loop=(1, 3, 2))
