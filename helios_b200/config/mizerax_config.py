@@ -11,7 +11,7 @@ or gives null.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from typing import Any, Dict, Optional, Tuple
 
 from .model_config import ConfigError
@@ -62,7 +62,7 @@ class MizeraxConfig:
     architecture: str
     vocab_size: int
     width: int
-    max_positions: int
+    max_positions: Optional[int]      # None until read off the checkpoint (rows of the position table)
     norm_eps: float
     residual_mult: float
     layers: Tuple[MizeraxLayer, ...]
@@ -93,7 +93,8 @@ class MizeraxConfig:
     def from_json(cls, cfg: Dict[str, Any]) -> "MizeraxConfig":
         vocab = _need(cfg, "vocab", "the file")
         width = _need(cfg, "width", "the file")
-        max_pos = _need(cfg, "max_positions", "the file")
+        # the number of learned positions may be left to the position table's shape
+        max_pos = _need(cfg, "max_positions", "the file") if cfg.get("max_positions") is not None else None
         eps = _need(cfg.get("norm"), "eps", "norm", float)
         mult = _need(cfg, "residual_mult", "the file", float) if "residual_mult" in cfg else 1.0
         layers = cfg.get("layers")
@@ -113,6 +114,16 @@ class MizeraxConfig:
         return cls(architecture=str(cfg.get("architecture", "Mizerax")), vocab_size=vocab, width=width,
                    max_positions=max_pos, norm_eps=eps, residual_mult=mult, layers=tuple(out), loop=loop,
                    eos_token_ids=eos_ids)
+
+
+def fill_from_tensor_shapes(cfg: MizeraxConfig, shapes: Dict[str, Tuple[int, ...]]) -> MizeraxConfig:
+    """Sizes the file leaves out, read off the checkpoint's tensor shapes."""
+    if cfg.max_positions is None:
+        pos = shapes.get("pos")
+        if pos is None or len(pos) != 2:
+            raise ConfigError("config.json has no 'max_positions' and the checkpoint no position table 'pos'")
+        cfg = replace(cfg, max_positions=int(pos[0]))
+    return cfg
 
 
 def _attention(mx, where) -> SinkAttentionConfig:
@@ -155,6 +166,7 @@ def _loop(lp, n_layers: int) -> Optional[LoopConfig]:
         if not isinstance(v, int) or isinstance(v, bool) or v < 0:
             raise ConfigError(f"config.json: loop.{key} must be a count, got {v!r}")
     start, stop, times = lp["start"], lp["stop"], lp["times"]
-    if not start < stop <= n_layers or times < 1:
+    if not start <= stop <= n_layers:
         raise ConfigError(f"config.json: loop {start}..{stop} x {times} does not fit {n_layers} layers")
-    return LoopConfig(start, stop, times)
+    # an empty stretch runs nothing, whatever the count; a count of 0 leaves the stretch's layers out
+    return LoopConfig(start, stop, times) if stop > start else None

@@ -13,7 +13,7 @@ the layers and all sizes are the file's.
 """
 from __future__ import annotations
 
-from ..config.mizerax_config import MizeraxConfig
+from ..config.mizerax_config import MizeraxConfig, fill_from_tensor_shapes
 from ..config.registry import register_architecture
 from ..parts import ModelPlan, OutputHead, Run, TokenEmbedding, distance_slopes, part_class
 from ..parts.stream import StreamInputMix
@@ -24,6 +24,9 @@ LOOP_STAGE = "loop."
 
 
 def build_mizerax_plan(cfg: MizeraxConfig) -> ModelPlan:
+    if cfg.max_positions is None:
+        raise ValueError("the number of learned positions is neither in config.json ('max_positions') "
+                         "nor read off a checkpoint")
     norm_cls = part_class("norm", "layernorm")
     block_cls = part_class("block", "parallel")
     mixer_cls = part_class("mixer", "sink_gqa_attention")
@@ -48,6 +51,7 @@ def build_mizerax_plan(cfg: MizeraxConfig) -> ModelPlan:
         layers.append(block_cls(norm(), mixer, ffn, mult=cfg.residual_mult, layer_scale=True))
         prefixes.append(f"l{i}.")
     schedule = [Run(i, before=LOOP_STAGE if begins else None) for i, begins in cfg.layer_runs()]
+    looped = any(begins for _i, begins in cfg.layer_runs())
     return ModelPlan(
         config=cfg,
         embedding=TokenEmbedding(cfg.vocab_size, cfg.width, tensor_name=""),
@@ -62,8 +66,9 @@ def build_mizerax_plan(cfg: MizeraxConfig) -> ModelPlan:
         final_norm_prefix="final.norm",
         head_prefix="head",
         tied={"head": "embed"},
-        benign_suffixes=(),
-        stages={LOOP_STAGE: StreamInputMix(cfg.width, tensor_name="in")} if cfg.loop else {},
+        # a file whose loop runs nothing may still bring the loop's matrix
+        benign_suffixes=() if looped else (LOOP_STAGE + "in",),
+        stages={LOOP_STAGE: StreamInputMix(cfg.width, tensor_name="in")} if looped else {},
     )
 
 
@@ -92,4 +97,4 @@ def _toy_config(sizes):
 
 
 register_architecture("Mizerax", MizeraxConfig.from_json, build_mizerax_plan, toy_config=_toy_config,
-                      replace=True)
+                      sizes_from_tensors=fill_from_tensor_shapes, replace=True)

@@ -196,6 +196,12 @@ def test_configuration_is_read_layer_by_layer_and_faults_name_the_key():
     assert b.residual_mult == 1.0 and b.layers[0].mlp.identity == 0 and b.layers[1].mlp.identity == 0
     assert [i for i, _ in b.layer_runs()] == [0, 0, 0, 1, 2]
     assert arch.parse_config(MZ_ALONE["attention_only"]).loop is None
+    empty = copy.deepcopy(MZ_A)
+    empty["loop"] = {"start": 2, "stop": 2, "times": 3}
+    assert [i for i, _ in arch.parse_config(empty).layer_runs()] == [0, 1, 2, 3]
+    empty["loop"] = {"start": 1, "stop": 3, "times": 0}
+    none = arch.parse_config(empty)
+    assert [i for i, _ in none.layer_runs()] == [0, 3] and not arch.build_plan(none).stages
     for path, value, word in ((("layers", 0, "type"), "conv_mixer", "type"),
                               (("layers", 1, "mixer", "kv_heads"), 2, "kv_heads"),
                               (("layers", 0, "mlp", "router", "top"), 9, "top"),
@@ -255,6 +261,18 @@ def test_toy_model_of_the_design_from_the_command_line(tmp_path):
     assert main(["info", "--model", str(out)]) == 0
     logits, _ = pm.forward(cfg, weights, [1, 2, 3])
     assert logits.shape == (3, 120) and torch.isfinite(logits).all()
+
+
+def test_the_number_of_positions_may_come_from_the_position_table(tmp_path):
+    from helios_b200.config.registry import load_config
+    from helios_b200.weights import write_model_folder
+
+    folder = write_model_folder(tmp_path / "m", MZ_ALONE["looped"], 3)
+    stripped = copy.deepcopy(MZ_ALONE["looped"])
+    del stripped["max_positions"]
+    with open(folder / "config.json", "w") as f:
+        json.dump(stripped, f)
+    assert load_config(folder).max_positions == 200
 
 
 def test_the_plain_model_decodes_as_it_prefills():
