@@ -345,15 +345,19 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
       qk_tile<HD, DEC_TILE / 8>(s, qa, kt, lane);
       const int tile_key0 = first + tile * DEC_TILE;
       if (opt.slopes != nullptr) {
-        // a bias that grows with the distance, for every row (head) of the tile; and the masks
+        // a bias that grows with the distance, for every row (head) of the tile: its value at
+        // this thread's first key of the tile, then a constant step per key; masks only in
+        // the last tile (keys beyond the token's own) and the first (keys before the window)
         const int key0 = tile_key0 + 2 * (lane & 3);
+        const float at0[2] = {-slope_log2[0] * (float)(pos - key0), -slope_log2[1] * (float)(pos - key0)};
+        const bool edge = tile_key0 + DEC_TILE > k_end || tile_key0 < lo;
 #pragma unroll
         for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
+          for (int e = 0; e < (WIDE ? 4 : 2); ++e) {
+            const float v = fmaf(s[nt][e], scale_log2, fmaf(slope_log2[e >> 1], (float)(nt * 8 + (e & 1)), at0[e >> 1]));
             const int key = key0 + nt * 8 + (e & 1);
-            s[nt][e] = (key < k_end && key >= lo)
-                ? fmaf(s[nt][e], scale_log2, -slope_log2[e >> 1] * (float)(pos - key)) : -INFINITY;
+            s[nt][e] = (!edge || (key < k_end && key >= lo)) ? v : -INFINITY;
           }
         }
       } else if (tile_key0 + DEC_TILE > k_end || tile_key0 < lo) {
